@@ -1,6 +1,6 @@
 """Single-kernel cases on synthetic inputs, for timing and for profiler captures.
 
-    python -m tritonllm_b200.cases <case> [--iters N] [--batch B] [--ctx L] [--rows R] [--window W]
+    python cases.py <case> [--iters N] [--batch B] [--ctx L] [--rows R] [--window W]
 
 Each case builds several independent copies of its inputs on the device (together larger than
 the 126 MB L2), warms up, captures one call per copy into a CUDA graph, then times `--iters`
@@ -18,13 +18,16 @@ import argparse
 import json
 import os
 import statistics
+import sys
 import time
 
 import torch
 
-from . import _lib, ops
+_ROOT = os.path.dirname(os.path.abspath(__file__))
+if _ROOT not in sys.path:
+    sys.path.insert(0, _ROOT)
 
-_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+from tritonllm_b200 import _lib, ops  # noqa: E402
 
 
 def _peak_gbs():
@@ -48,6 +51,22 @@ def _tensor_fields(flops, us):
     return {"tflops": round(tf, 1), "frac_of_bf16_peak": round(tf / peak, 3), "peak_tflops": peak}
 
 
+_REF = {}
+
+
+def _ref():
+    """The reference's own kernel entry points (a TritonLLM checkout under baseline/_ref or $TRITONLLM_REFERENCE),
+    for the `--reference` legs: the same inputs through the reference's Triton kernels on the same GPU."""
+    if not _REF:
+        from tritonllm_b200 import integration
+        M = integration.load_reference()
+        import gpt_oss.triton.triton_kernels as TK
+        from gpt_oss.triton import moe as RM
+        from triton_kernels.routing import routing
+        _REF.update(M=M, TK=TK, RM=RM, routing=routing)
+    return _REF
+
+
 def _bf(*shape, scale=1.0, dev="cuda"):
     return (torch.randn(*shape, device=dev, dtype=torch.float32) * scale).to(torch.bfloat16)
 
@@ -63,6 +82,10 @@ def build_case(name: str, a):
         sq = torch.tensor([L - 1], dtype=torch.int64, device=dev)
         vis = min(W, L) if W else L
         nbytes = B * vis * 8 * 64 * 2 * 2 + 2 * B * 64 * 64 * 2
+        if a.reference:
+            fn_ref = _ref()["M"].attention_decode
+            sinks_bf = sinks.bfloat16()
+            return (lambda: fn_ref(q, k, v, sinks_bf, 0.125, W, sq)), nbytes, f"B={B} ctx={L} window={W} (reference kernel)"
         return (lambda: ops.attention_decode(q, k, v, sinks, 0.125, W, sq)), nbytes, f"B={B} ctx={L} window={W}"
     if name in ("rmsnorm", "add_rmsnorm"):
         R = a.rows
@@ -70,7 +93,8 @@ def build_case(name: str, a):
         gain = torch.ones(2880, device=dev)
         y, h = torch.empty_like(x), torch.empty_like(x)
         if name == "rmsnorm":
-            return (lambda: ops.rmsnorm_forward(x, gain, 1e-5, out=y)), R * 2880 * 4 + 2880 * 4, f"rows={R} dim=2880"
+            fn = _ref()["TK"].rmsnorm_forward if a.reference else ops.rmsnorm_forward
+            return (lambda: fn(x, gain, 1e-5, out=y)), R * 2880 * 4 + 2880 * 4, f"rows={R} dim=2880"
         return (lambda: ops.add_rmsnorm_forward(x, d, gain, 1e-5, h_out=h, y_out=y)), R * 2880 * 8 + 2880 * 4, \
             f"rows={R} dim=2880"
     if name == "rope":
@@ -78,7 +102,8 @@ def build_case(name: str, a):
         q, k = _bf(1, R, 64, 64), _bf(1, R, 8, 64)
         cos, sin = ops.yarn_cos_sin(max(R, 16), device=dev)
         off = torch.zeros(1, dtype=torch.int64, device=dev)
-        return (lambda: ops.rope_forward(q, k, sin, cos, cos.shape[0], off)), R * 72 * 64 * 4 + R * 256, f"tokens={R}"
+        fn = _ref()["TK"].rope_forward if a.reference else ops.rope_forward
+        return (lambda: fn(q, k, sin, cos, cos.shape[0], off)), R * 72 * 64 * 4 + R * 256, f"tokens={R}"
     if name == "swiglu":
         R = a.rows
         x = _bf(R, 5760, scale=2.0)
@@ -95,15 +120,16 @@ def build_case(name: str, a):
         cos, sin = ops.yarn_cos_sin(ctx, device=dev)
         off = torch.tensor([5], dtype=torch.int64, device=dev)
         nbytes = 5120 * 2880 * 2 + B * 2880 * 2 + B * 5120 * 2 + 5120 * 2
-        return (lambda: ops.qkv_rope_cache_decode_forward(x, w, b, sin, cos, ctx, ck, cv, off, 64, 8, 64)), nbytes, \
-            f"B={B} hidden=2880 out=5120"
+        fn = _ref()["TK"].qkv_rope_cache_decode_forward if a.reference else ops.qkv_rope_cache_decode_forward
+        return (lambda: fn(x, w, b, sin, cos, ctx, ck, cv, off, 64, 8, 64)), nbytes, f"B={B} hidden=2880 out=5120"
     if name == "oproj_decode":
         B = a.batch
         x = _bf(B, 1, 4096)
         w, b = _bf(2880, 4096, scale=0.02), _bf(2880, scale=0.02)
         res = _bf(B, 1, 2880)
         nbytes = 2880 * 4096 * 2 + B * 4096 * 2 + 2 * B * 2880 * 2 + 2880 * 2
-        return (lambda: ops.out_residual_decode_forward(x, w, b, res)), nbytes, f"B={B} in=4096 out=2880"
+        fn = _ref()["TK"].out_residual_decode_forward if a.reference else ops.out_residual_decode_forward
+        return (lambda: fn(x, w, b, res)), nbytes, f"B={B} in=4096 out=2880"
     if name == "qkv_prefill":
         R = a.rows
         x = _bf(1, R, 2880)
@@ -157,6 +183,17 @@ def build_case(name: str, a):
         touched = int(torch.unique(idx.long()).numel())
         per_expert = (2 * I) * (H // 2 + H // 32 + 4) + H * (I // 2 + I // 32 + 4)
         nbytes = touched * per_expert + T * H * 2 * 2
+        if a.reference:  # moe_decode_experts: routing metadata + two matmul_ogs calls on weights its own quantiser laid out
+            R = _ref()
+            rw1, rw1s = R["RM"].quantize_mx4(_bf(E, H, 2 * I, scale=0.05))
+            rw2, rw2s = R["RM"].quantize_mx4(_bf(E, I, H, scale=0.05))
+            b1, b2 = torch.randn(E, 2 * I, device=dev) * 0.1, torch.randn(E, H, device=dev) * 0.1
+            expert_fn = R["RM"].moe_decode_experts if T <= 256 else R["RM"].moe_experts
+
+            def ref_moe():
+                rdata, gi, si = R["routing"](logits, 4, simulated_ep=1)
+                return expert_fn(x, rw1, rw1s, rw2, rw2s, b1, b2, rdata, gi, si)
+            return ref_moe, nbytes, f"T={T} E={E} touched={touched} hidden=2880 (reference routing + matmul_ogs)"
         return (lambda: ops.moe_experts_decode(x, vals, idx, w1, w2)), nbytes, f"T={T} E={E} touched={touched} hidden=2880 fp4={not a.no_fp4}"
     if name == "attn_prefill":
         B, T, W = a.batch, a.ctx, a.window
@@ -166,6 +203,9 @@ def build_case(name: str, a):
         sq = torch.zeros(1, dtype=torch.int64, device=dev)
         pairs = sum(min(i + 1, W) if W else i + 1 for i in range(T))  # visible (query, key) pairs per head
         fn = lambda: ops.attention(q, k, v, sinks, 0.125, W, sq)  # noqa: E731
+        if a.reference:  # attention_tt_tma.attention on cc >= 9: includes its host-side transposes, as the model pays them
+            fn_ref, sinks_bf = _ref()["M"].attention, sinks.bfloat16()
+            fn = lambda: fn_ref(q, k, v, sinks_bf, 0.125, W, sq)  # noqa: E731
         nbytes = B * T * 64 * 64 * 2 * 2 + 2 * B * T * 8 * 64 * 2
         return fn, nbytes, f"B={B} T={T} window={W}", 4.0 * B * 64 * 64 * pairs
     if name == "router":
@@ -259,7 +299,7 @@ def generate_case(a):
     """Whole-model greedy generation (BASELINE config 5 shape): `--batch` sequences with `--prompt` seeded random
     prompt tokens each are ingested into the KV store, then `--new-tokens` tokens per sequence are generated with
     the step replayed from one CUDA graph.  Random weights of the 20b architecture (`--layers`, `--moe-experts`)."""
-    from . import generate as G
+    from tritonllm_b200 import generate as G
     dev = "cuda"
     B, P, N = a.batch, a.prompt, a.new_tokens
     cfg = G.ModelConfig(num_hidden_layers=a.layers, num_experts=a.moe_experts or 32)
@@ -299,7 +339,7 @@ def generate_case(a):
                       "distinct_tokens": int(out.unique().numel())}))
 
 
-def main():
+def _parser():
     ap = argparse.ArgumentParser()
     ap.add_argument("case")
     ap.add_argument("--iters", type=int, default=20)
@@ -320,18 +360,24 @@ def main():
                     help="generate: fill the KV store with random values instead of ingesting the prompt")
     ap.add_argument("--library", action="store_true",
                     help="GEMM cases: time torch's cuBLAS path on the same shape instead (the library comparator)")
+    ap.add_argument("--reference", action="store_true",
+                    help="time the reference's own Triton kernel for the case instead (attn_decode, attn_prefill, moe_decode, "
+                         "rmsnorm, rope, qkv_decode, oproj_decode); needs a TritonLLM checkout and triton")
     ap.add_argument("--tune", action="append", default=[], help="name=value tuning knob (b2_set_tunable)")
-    a = ap.parse_args()
-    assert torch.cuda.is_available(), "cases need a CUDA device"
-    lib = _lib.load()
-    for kv in a.tune:
-        name, val = kv.split("=")
-        _lib.check("b2_set_tunable", lib.b2_set_tunable(name.encode(), int(val)))
-    if a.case == "generate":
-        return generate_case(a)
-    if a.case == "decode_stack":
-        decode_stack(a)
-        return
+    return ap
+
+
+def make_args(case: str, **kw):
+    """The argument namespace of one case with the command line's defaults, for callers that time cases in-process."""
+    a = _parser().parse_args([case])
+    for k, v in kw.items():
+        assert hasattr(a, k), k
+        setattr(a, k, v)
+    return a
+
+
+def run_case(a) -> dict:
+    """Times one single-kernel case as the module docstring describes and returns the result record."""
     built = build_case(a.case, a)
     fn, nbytes, desc = built[:3]
     flops = built[3] if len(built) > 3 else None
@@ -349,9 +395,16 @@ def main():
     if not a.no_graph:
         # replaying a captured window takes the host (Python, ctypes, launch set-up) out of the measurement
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            for f in fns:
-                f()
+        try:
+            with torch.cuda.graph(graph):
+                for f in fns:
+                    f()
+        except Exception as exc:   # only the reference legs can get here (a host synchronisation inside the op)
+            if not a.reference:
+                raise
+            print(f"# capture failed ({exc!r:.200}); timing eager launches", file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
         stream = torch.cuda.current_stream()
     times = []
     for _ in range(a.iters):
@@ -374,10 +427,26 @@ def main():
     us = statistics.median(times)
     peak, kind = _peak_gbs()
     gbs = nbytes / us / 1e3
-    print(json.dumps({"case": a.case, "shape": desc, "algorithmic_bytes": nbytes, "us_median": round(us, 2),
-                      "us_min": round(min(times), 2), "gbs": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 3),
-                      "peak_gbs": peak, "peak_kind": kind, "iters": a.iters, "calls_per_window": n_copies, "graph": graph is not None,
-                      "tune": a.tune, "library": bool(a.library), **_tensor_fields(flops, us)}))
+    return {"case": a.case, "shape": desc, "algorithmic_bytes": nbytes, "us_median": round(us, 2),
+            "us_min": round(min(times), 2), "gbs": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 3),
+            "peak_gbs": peak, "peak_kind": kind, "iters": a.iters, "calls_per_window": n_copies, "graph": graph is not None,
+            "tune": a.tune, "library": bool(a.library), "reference_kernel": bool(a.reference),
+            "algorithmic_flops": flops, **_tensor_fields(flops, us)}
+
+
+def main():
+    a = _parser().parse_args()
+    assert torch.cuda.is_available(), "cases need a CUDA device"
+    lib = _lib.load()
+    for kv in a.tune:
+        name, val = kv.split("=")
+        _lib.check("b2_set_tunable", lib.b2_set_tunable(name.encode(), int(val)))
+    if a.case == "generate":
+        return generate_case(a)
+    if a.case == "decode_stack":
+        decode_stack(a)
+        return
+    print(json.dumps(run_case(a)))
 
 
 if __name__ == "__main__":

@@ -104,6 +104,10 @@ def call(fn: str, *args) -> None:
 
 
 def device_status(reset: bool = True) -> int:
+    """The per-device status word (0 = no kernel has recorded a failure); synchronises the device.  The word is
+    cleared only when it was non-zero, so the common case costs one 4-byte read."""
     out = _i32(0)
-    check("b2_device_status", load().b2_device_status(1 if reset else 0, C.byref(out)))
+    check("b2_device_status", load().b2_device_status(0, C.byref(out)))
+    if out.value and reset:
+        check("b2_device_status", load().b2_device_status(1, C.byref(_i32(0))))
     return out.value

@@ -73,8 +73,8 @@ __global__ void __launch_bounds__(1024) moe_route_kernel(const int16_t* __restri
     const int t = sl / MOE_TOPK, e = topk_idx[sl];
     if (e < 0 || e >= n_experts)
       atomicOr(status, B2_DEV_BAD_INDEX);
-    else
-      atomicOr(&mask[e][t >> 5], 1u << (t & 31));
+    else if (atomicOr(&mask[e][t >> 5], 1u << (t & 31)) & (1u << (t & 31)))
+      atomicOr(status, B2_DEV_BAD_INDEX);   // the same expert twice for one token: the lists would count it once
   }
   __syncthreads();
   if (tid < 32) {  // counts and exclusive offsets, one warp
@@ -572,7 +572,6 @@ constexpr int FP4_A_BYTES = MOE_FT * FP4_KB;      // 16 KiB in shared memory (8 
 constexpr int FP4_A_TX = MOE_FT * FP4_KB / 2;     // bytes the TMA transaction counts for it
 constexpr int FP4_MAX_STAGES = 8;
 constexpr int FP4_THREADS = 192;
-constexpr int FP4_TOK = 64;   // most tokens of one expert per CTA: keeps the accumulator at 128 columns, so two CTAs share an SM
 
 struct MoeFp4Args {
   const uint8_t* sfa;       // [E][tiles][nkb][512]

@@ -23,7 +23,7 @@ from dataclasses import dataclass, field
 
 import torch
 
-from . import ops
+from . import _lib, ops
 
 _OFF = {"0", "false", "no", "off", ""}
 
@@ -90,6 +90,9 @@ class Cache:
         """Drops the oldest entries and keeps the newest ``keep_last_n`` (default: capacity - slide_chunk)
         at the front of the store; returns the new position.  Same arithmetic as model.py:391-424."""
         if current is None:
+            if not self.owns_offset:
+                # the owner of a shared counter has already moved it when the loop reaches this layer
+                raise ValueError("this Cache shares its position counter: pass `current` (the position before the slide)")
             current = int(self.offset.item())
         capacity = self.k.shape[1]
         if current < capacity or not self.can_slide():
@@ -104,6 +107,17 @@ class Cache:
 
     def batch_slice(self, b0: int, b1: int) -> "_CacheView":
         return _CacheView(self.k[b0:b1], self.v[b0:b1], self.offset)
+
+
+def check_device_status(where: str) -> None:
+    """Raises B2Error when a kernel of this process has recorded a failure in the per-device status word since the
+    last check (a bounded wait that gave up, a token id or expert index out of range): such a kernel carries on
+    with defined but wrong data, so the results produced since the last check must not be used.  Reads one word
+    from the device; call it after a synchronisation point, not inside a captured step."""
+    code = _lib.device_status()
+    if code:
+        raise _lib.B2Error(where, code, f"device status word 0x{code:x} (0x1/0x2/0x4/0x8: a bounded wait gave up; "
+                                        "0x10: an index was out of range)")
 
 
 @dataclass
@@ -431,6 +445,7 @@ class TokenGenerator:
             self.model.prefill(prompts[:, :-1], self.caches)
             torch.cuda.synchronize(self.device)
             prefill_elapsed = time.perf_counter() - t0
+            check_device_status("prefill")
         self.input_token.copy_(prompts[:, -1:])
         greedy = temperature == 0.0 and not return_logprobs
         need_host = bool(stop) or return_logprobs or enable_repeat_pattern_stop
@@ -452,6 +467,7 @@ class TokenGenerator:
             if return_logprobs:
                 lp = torch.log_softmax(out, dim=-1).gather(1, ids.view(-1, 1))[:, 0].tolist()
             ids_host = ids.tolist()
+            check_device_status("generate")   # the copy above has synchronised; a failed step must not be yielded
             if self.batch_size == 1:
                 yield (ids_host[0], lp[0]) if return_logprobs else ids_host[0]
             else:
@@ -468,6 +484,7 @@ class TokenGenerator:
                 if all(finished):
                     break
         torch.cuda.synchronize(self.device)
+        check_device_status("generate")
         self.last_generation_stats = {"generated_tokens": produced, "prefill_time_s": prefill_elapsed,
                                       "decode_time_s": time.perf_counter() - t0, "loop_detected": loop_detected}
 
@@ -487,9 +504,12 @@ class TokenGenerator:
         for i in range(new_tokens):
             can_continue, decode_offset = self._handle_kv_capacity(decode_offset)
             if not can_continue:
-                return out[:, :i]
+                out = out[:, :i]
+                break
             ids = self._step(True)
             self.input_token.copy_(ids.view(-1, 1))
             out[:, i].copy_(ids)
             decode_offset += 1
+        torch.cuda.synchronize(self.device)
+        check_device_status("generate_greedy")
         return out

@@ -6,6 +6,13 @@ forwards to the C ABI of ``libtritonllm_b200.so`` on torch's current stream.
 Tensors must be CUDA tensors; there is no CPU path.  Outputs come from a
 shape-keyed scratch pool like the reference's, so addresses are stable across
 CUDA-graph replays.
+
+One stream at a time: pooled outputs and the workspaces of ``attention_decode``
+(arrival counters, split-KV partials), ``moe_experts_decode`` and the
+unembedding are process-global, keyed by shape and device like the reference's
+pool, not by stream.  Calls of the same shape that overlap on the GPU (two
+streams, two threads, two generators stepping concurrently) would share them
+and corrupt each other's results; run them on one stream or serialise them.
 """
 from __future__ import annotations
 
@@ -240,13 +247,18 @@ def topk(x, k, apply_softmax=True, dim=1, return_bitmatrix=True, y_indx=None, n_
 
 # --------------------------------------------------------------------------- patching
 REPLACED = ("rmsnorm_forward", "rope_forward", "qkv_rope_cache_decode_forward", "out_residual_decode_forward",
-            "attention_decode", "attention", "unembedding_decode_forward", "unembedding_decode_argmax_forward")
+            "attention_decode", "attention", "unembedding_decode_forward", "unembedding_decode_argmax_forward",
+            "moe", "moe_decode")
 
 
 def patch(model_module) -> list[str]:
     """Rebinds the op names that ``tritonllm.gpt_oss.triton.model`` imported
     (model.py:11-34) to the functions of this module, so the reference's
-    RMSNorm / RotaryEmbedding / AttentionBlock modules call the B200 kernels.
+    RMSNorm / RotaryEmbedding / AttentionBlock / MLPBlock modules call the B200
+    kernels: after it ``TransformerBlock.forward`` (model.py:891-894) launches no
+    Triton kernel.  (The dense prefill projections stay the ``F.linear`` calls of
+    QKV.forward / OUT.forward; ``qkv_rope_prefill`` / ``out_residual_forward`` are
+    the fused forms for a caller that edits those two methods.)
     Returns the names that were rebound."""
     done = []
     for name in REPLACED:
@@ -488,6 +500,7 @@ class ExpertWeightsFp4:
 
 
 _moe_ws: dict = {}
+_moe_generation: dict = {}   # workspace address -> number of expert calls that have written it
 
 
 class PendingMoe:
@@ -496,6 +509,7 @@ class PendingMoe:
 
     def __init__(self, ws, tokens, hidden, inter):
         self.ws, self.tokens, self.hidden, self.inter = ws, tokens, hidden, inter
+        self.generation = _moe_generation.get(ws.data_ptr(), 0)
 
 
 def moe_combine_add_rmsnorm(pending: PendingMoe, residual, scale, eps, h_out=None, y_out=None):
@@ -504,6 +518,9 @@ def moe_combine_add_rmsnorm(pending: PendingMoe, residual, scale, eps, h_out=Non
     ``add_rmsnorm_forward``.  residual [..., hidden] bf16 with pending.tokens rows; h_out may be residual."""
     _need_cuda(residual, scale)
     hidden = pending.hidden
+    if _moe_generation.get(pending.ws.data_ptr(), 0) != pending.generation:
+        raise RuntimeError("the expert outputs of this PendingMoe were overwritten by a later moe_experts_decode call "
+                           "of the same size: combine a deferred call before the next one")
     assert residual.dtype == _BF16 and residual.shape[-1] == hidden and residual.stride(-1) == 1
     r2 = residual.reshape(-1, hidden)
     assert r2.shape[0] == pending.tokens and scale.dtype == torch.float32 and scale.shape == (hidden,)
@@ -549,6 +566,7 @@ def moe_experts_decode(x, topk_vals, topk_idx, w1, w2, alpha=1.702, limit=7.0, d
               w1.bias.data_ptr(), w2.codes.data_ptr(), (w2.sf if fp4 else w2.scales).data_ptr(), w2.bias.data_ptr(),
               _ptr(out), hidden if out is None else out.stride(0), ws.data_ptr(), ws.numel(), t, e, hidden, inter,
               float(alpha), float(limit), _stream())
+    _moe_generation[ws.data_ptr()] = _moe_generation.get(ws.data_ptr(), 0) + 1
     return PendingMoe(ws, t, hidden, inter) if defer_combine else out
 
 
@@ -631,3 +649,70 @@ def kv_zero_tail(k, v, start: int) -> None:
     """Zeroes tokens start .. n_ctx-1 of every sequence (``Cache.truncate`` / ``Cache.reset``, model.py:354-371)."""
     batch, n_ctx, row_bytes = _kv_rows(k, v)
     _lib.call("b2_kv_zero_tail", k.data_ptr(), v.data_ptr(), batch, n_ctx, row_bytes, int(start), _stream())
+
+
+# ------------------------------------------------------------------ MoE block behind the reference's call sites
+_expert_repack: dict[int, tuple] = {}   # id(reference weight) -> (weight, scales, ExpertWeightsFp4)
+
+
+def _raw(t):
+    """The torch tensor inside one of the reference's wrapped tensors (triton_kernels/tensor.py:99-160)."""
+    st = getattr(t, "storage", None)
+    if st is not None and not isinstance(t, torch.Tensor):
+        return st.data if hasattr(st, "data") else st
+    return t
+
+
+def experts_from_reference(w, w_mx, bias) -> "ExpertWeightsFp4":
+    """The kernels' weight layout from what MLPBlock holds (model.py:627-667, 973-989): ``w`` is the wrapped
+    MXFP4 value tensor of logical shape [E, K, N] whose uint8 storage is [E, K/2 (+ padding to 128 on
+    Blackwell, blackwell_value.py:12-24), N] with K contiguous, ``w_mx`` the wrapped E8M0 scales [E, K/32, N],
+    ``bias`` [E, N] (the bf16 parameter or its fp32 cache).  Repacked once per weight object."""
+    hit = _expert_repack.get(id(w))
+    if hit is not None and hit[0] is w and hit[1] is w_mx:
+        return hit[2]
+    data, scales = _raw(w), _raw(w_mx)
+    k = int(w.shape[-2]) if not isinstance(w, torch.Tensor) else 2 * data.shape[-2]
+    assert data.dtype == torch.uint8 and data.dim() == 3 and k % 32 == 0 and data.shape[1] >= k // 2
+    packed = ExpertWeightsFp4(ExpertWeights.from_reference(data[:, : k // 2], scales[:, : k // 32], bias))
+    _expert_repack[id(w)] = (w, w_mx, packed)
+    return packed
+
+
+def _moe_from_reference(x, wg, w1, w1_mx, w2, w2_mx, bg, b1, b2, experts_per_token, swiglu_limit):
+    if x.numel() == 0:
+        return x
+    assert x.dim() == 2
+    logits = router_logits(x, wg, bg)
+    vals, idx, _ = topk(logits, experts_per_token)
+    e1, e2 = experts_from_reference(w1, w1_mx, b1), experts_from_reference(w2, w2_mx, b2)
+    return moe_experts(x, vals, idx, e1, e2, limit=swiglu_limit)
+
+
+def moe_experts(x, topk_vals, topk_idx, w1, w2, alpha=1.702, limit=7.0):
+    """moe_experts (tritonllm/gpt_oss/triton/moe.py:54-87) for any number of tokens: the expert GEMMs of
+    x [T, hidden] with the routing `topk` returned, in calls of at most 2048 tokens."""
+    t = x.shape[0]
+    block = 2048 if isinstance(w1, ExpertWeightsFp4) else 256
+    if t <= block:
+        return moe_experts_decode(x, topk_vals, topk_idx, w1, w2, alpha=alpha, limit=limit)
+    out = torch.empty_like(x)
+    for r0 in range(0, t, block):
+        r1 = min(t, r0 + block)
+        out[r0:r1] = moe_experts_decode(x[r0:r1], topk_vals[r0:r1], topk_idx[r0:r1], w1, w2, alpha=alpha, limit=limit)
+    return out
+
+
+def moe(x, wg, w1, w1_mx, w2, w2_mx, bg, b1, b2, experts_per_token=4, num_experts=128, swiglu_limit=7.0,
+        fused_act=True, interleaved=True):
+    """Drop-in for moe (tritonllm/gpt_oss/triton/moe.py:90-95): router matmul + bias, top-k with softmax, expert
+    GEMMs with the fused clamped SwiGLU, weighted sum.  Takes the reference's wrapped weight tensors."""
+    assert interleaved, "gate / linear features are interleaved in the checkpoint layout"
+    return _moe_from_reference(x, wg, w1, w1_mx, w2, w2_mx, bg, b1, b2, experts_per_token, swiglu_limit)
+
+
+def moe_decode(x, wg, w1, w1_mx, w2, w2_mx, bg, b1, b2, experts_per_token=4, num_experts=128, swiglu_limit=7.0,
+               fused_act=True, interleaved=True):
+    """Drop-in for moe_decode (tritonllm/gpt_oss/triton/moe.py:178-205); same contract as :func:`moe`."""
+    assert interleaved, "gate / linear features are interleaved in the checkpoint layout"
+    return _moe_from_reference(x, wg, w1, w1_mx, w2, w2_mx, bg, b1, b2, experts_per_token, swiglu_limit)
