@@ -380,6 +380,38 @@ def decode_run(model, dev, rank: int, batch: int, hbm_peak: float):
             "gbs": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / hbm_peak, "sequences_per_gpu": batch}
 
 
+HEADSHARD_T = 8192
+
+
+def headshard_leg(dev, rank: int, world: int):
+    """Optional long-context mode: the attention block of ONE 8192-token sequence with its heads split over the ranks
+    (each rank: norm, its slice of QKV + RoPE, its heads' prefill attention; one NCCL all-gather of [T, 4096 / N]
+    bf16 per rank; o_proj + residual replicated).  Full-causal layer.  Returns ms per block and the all-gather's part."""
+    from tritonllm_b200 import headshard, ops
+    gd = torch.Generator(device=dev).manual_seed(77)   # the same weights and input on every rank
+    r = lambda *s, sc=1.0: (torch.randn(*s, generator=gd, device=dev) * sc).to(torch.bfloat16)  # noqa: E731
+    x = r(1, HEADSHARD_T, 2880)
+    gain = torch.ones(2880, device=dev)
+    wqkv, bqkv, wo, bo, sinks = r(5120, 2880, sc=0.02), r(5120, sc=0.02), r(2880, 4096, sc=0.02), r(2880, sc=0.02), r(64)
+    cos, sin = ops.yarn_cos_sin(HEADSHARD_T, device=dev)
+    shard = headshard.shard_attention_weights(wqkv, bqkv, sinks, rank, world)
+    for _ in range(3):
+        headshard.attention_block_headsharded(x, gain, shard, wo, bo, sin, cos, HEADSHARD_T, SCALE, 0)
+    torch.cuda.synchronize()
+    total, gather = [], []
+    for _ in range(8):
+        tm = {}
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        headshard.attention_block_headsharded(x, gain, shard, wo, bo, sin, cos, HEADSHARD_T, SCALE, 0, timings=tm)
+        e1.record()
+        torch.cuda.synchronize()
+        total.append(e0.elapsed_time(e1))
+        gather.append(tm["gather_start"].elapsed_time(tm["gather_end"]))
+    total.sort(), gather.sort()
+    return total[len(total) // 2], gather[len(gather) // 2]
+
+
 def run_b200(args, rank: int, world: int, local_rank: int):
     from tritonllm_b200 import _lib, ops, sharding
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
@@ -535,13 +567,22 @@ def run_b200(args, rank: int, world: int, local_rank: int):
             decode_err = repr(exc)[:300]
         barrier()
 
+    hs_ms, hs_gather, hs_err = 1e30, 1e30, None
+    if not args.no_headshard and 8 % world == 0:
+        try:
+            barrier()
+            hs_ms, hs_gather = headshard_leg(dev, rank, world)
+        except Exception as exc:
+            hs_err = repr(exc)[:300]
+        barrier()
+
     def dms(kind, key):
         v = decode.get(kind, {}).get(key)
         return v if v is not None else 1e30
 
-    ms_total, e2e_ms, res_ms, full_ms, window_ms, dw, dwp, ds, dsp = sharding.max_over_ranks(
+    ms_total, e2e_ms, res_ms, full_ms, window_ms, dw, dwp, ds, dsp, hs_ms, hs_gather = sharding.max_over_ranks(
         [ms_total, e2e_ms, res_ms, full_ms, window_ms, dms("weak", "ms_per_step"), dms("weak", "prefill_ms"),
-         dms("strong", "ms_per_step"), dms("strong", "prefill_ms")], device=dev)
+         dms("strong", "ms_per_step"), dms("strong", "prefill_ms"), hs_ms, hs_gather], device=dev)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -604,6 +645,13 @@ def run_b200(args, rank: int, world: int, local_rank: int):
                 dec["strong"] = dict(dec["weak"], note="one GPU: the strong and the weak split are the same run")
             dec["tokens_per_s"], dec["ms_per_step"] = dec["weak"]["tokens_per_s"], dw
         out["decode"] = dec
+    if not args.no_headshard and 8 % world == 0:
+        out["prefill_headshard"] = {
+            "ms_per_block": hs_ms if hs_ms < 1e29 else None, "ms_all_gather": hs_gather if hs_gather < 1e29 else None,
+            "all_gather_share": hs_gather / hs_ms if hs_ms < 1e29 else None, "tokens": HEADSHARD_T, "kv_heads_per_gpu": 8 // world,
+            "all_gather_bytes_per_rank": HEADSHARD_T * (4096 // world) * 2 if world > 1 else 0, "error": hs_err,
+            "workload": "one full-causal attention block (norm, QKV + RoPE, attention, o_proj + residual) of one "
+                        f"{HEADSHARD_T}-token sequence, heads split over the GPUs, one NCCL all-gather before o_proj; max over ranks"}
     if world == 1:
         out["cpu_baseline"] = cpu_baseline_leg()
         if not args.no_interpreter:
@@ -621,6 +669,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "interpreter-child"])
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-model decode tokens/s leg")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel roofline table")
+    ap.add_argument("--no-headshard", action="store_true", help="skip the head-sharded long-context prefill leg")
     ap.add_argument("--no-interpreter", action="store_true", help="skip the Triton-interpreter CPU leg")
     args = ap.parse_args()
     if args.impl == "interpreter-child":

@@ -98,6 +98,23 @@ int b2_qkv_rope_kv_decode(const void* hidden, int64_t hidden_stride_b, const voi
                           int64_t cache_stride_h, int64_t cache_ctx, int64_t batch, int hidden_size, int n_q_heads,
                           int n_kv_heads, int head_dim, int64_t max_ctx, void* stream);
 
+/* The same with one position per sequence and, optionally, a paged KV store - what a batched server needs
+ * (the reference keeps ONE position for the whole batch, model.py:344, 487, so it has no counterpart of this
+ * form; the arithmetic is that of qkv_rope_cache_decode_forward, triton_kernels.py:1109-1255).
+ * positions_dev: int64 [batch]; sequence b's q and k are rotated at positions_dev[b] % max_ctx and its K/V row
+ * goes to token positions_dev[b] of its own store.  block_table == NULL: kv_k / kv_v are [batch, kv_ctx, heads, 64]
+ * at the given strides.  block_table int32 [batch, table_stride] (page_size > 0): kv_k / kv_v are a pool of pages
+ * [pages, page_size, heads, 64], kv_stride_b is the page stride, and token p of sequence b lives in page
+ * block_table[b][p / page_size], row p % page_size; kv_ctx (<= table_stride * page_size) is the capacity of a
+ * sequence.  A position outside [0, kv_ctx) or an unmapped (negative) page writes no K/V and records
+ * B2_DEV_BAD_INDEX. */
+int b2_qkv_rope_kv_decode_ragged(const void* hidden, int64_t hidden_stride_b, const void* weight, const void* bias,
+                                 const float* sin_tab, const float* cos_tab, const int64_t* positions_dev, void* q_out,
+                                 void* kv_k, void* kv_v, int64_t kv_stride_b, int64_t kv_stride_n, int64_t kv_stride_h,
+                                 int64_t kv_ctx, const int32_t* block_table, int64_t table_stride, int page_size,
+                                 int64_t batch, int hidden_size, int n_q_heads, int n_kv_heads, int head_dim,
+                                 int64_t max_ctx, void* stream);
+
 /* ---- decode: o_proj + bias + residual, written into the residual -------------
  * residual[b,:] = t[b,:] @ W^T + bias + residual[b,:]   (one rounding to bf16).
  * Replaces out_residual_decode_forward / out_residual_decode_kernel
@@ -174,6 +191,19 @@ int b2_attn_decode(const void* q, const void* k, const void* v, const void* sink
                    int64_t batch, int n_kv_heads, int group, int head_dim, int64_t n_kv_ctx, int64_t kv_stride_b,
                    int64_t kv_stride_n, int64_t kv_stride_h, float sm_scale, int window, const void* start_q_dev,
                    int start_q_is_i64, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Decode attention with one position per sequence and, optionally, a paged KV store (same role as
+ * b2_qkv_rope_kv_decode_ragged; the arithmetic is that of attention_decode, attention_tt_decode.py:291-408).
+ * positions_dev: int32 or int64 [batch]; sequence b sees keys [lo_b, hi_b) computed from its own position.
+ * block_table == NULL: k / v as in b2_attn_decode.  Otherwise k / v are a pool [n_pages, page_size, heads, 64]
+ * (kv_stride_b = page stride), block_table int32 [batch, table_stride], page_size a multiple of 32, and n_kv_ctx
+ * (<= table_stride * page_size) the capacity of a sequence; an unmapped (negative) page that the visible range
+ * reaches records B2_DEV_BAD_INDEX.  batch <= 2048.  Workspace as for b2_attn_decode (same size function). */
+int b2_attn_decode_ragged(const void* q, const void* k, const void* v, const void* sinks, int sinks_is_f32, void* out,
+                          int64_t batch, int n_kv_heads, int group, int head_dim, int64_t n_kv_ctx, int64_t kv_stride_b,
+                          int64_t kv_stride_n, int64_t kv_stride_h, float sm_scale, int window, const void* positions_dev,
+                          int positions_are_i64, const int32_t* block_table, int64_t table_stride, int page_size,
+                          int64_t n_pages, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Decode attention for callers that cannot allocate device memory (a process whose
  * memory is carved up in advance, a plugin under a runtime that owns the allocator):

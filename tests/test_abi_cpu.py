@@ -76,10 +76,41 @@ def test_ops_refuse_cpu_tensors():
 def test_patch_rebinds_reference_names():
     import types
     from tritonllm_b200 import ops
-    fake = types.SimpleNamespace(rmsnorm_forward=1, rope_forward=2, attention_decode=3, unrelated=4)
+    fake = types.SimpleNamespace(rmsnorm_forward=1, rope_forward=2, attention_decode=3, moe=5, moe_decode=6, unrelated=4)
     done = ops.patch(fake)
-    assert set(done) == {"rmsnorm_forward", "rope_forward", "attention_decode"}
-    assert fake.rmsnorm_forward is ops.rmsnorm_forward and fake.unrelated == 4
+    assert set(done) == {"rmsnorm_forward", "rope_forward", "attention_decode", "moe", "moe_decode"}
+    assert fake.rmsnorm_forward is ops.rmsnorm_forward and fake.moe_decode is ops.moe_decode and fake.unrelated == 4
+
+
+def test_shared_position_counter_needs_the_position_to_slide():
+    """The reference's loop `for c in caches: c.slide_window()` reads each cache's own counter; with one counter
+    shared by all layers only its owner may do that - the others must be told the position."""
+    import torch
+    from tritonllm_b200.generate import Cache
+    first = Cache(1, 8, 2, 4, device=torch.device("cpu"))
+    other = Cache(1, 8, 2, 4, device=torch.device("cpu"), offset=first.offset)
+    assert first.owns_offset and not other.owns_offset
+    with pytest.raises(ValueError, match="pass `current`"):
+        other.slide_window()
+    assert other.slide_window(current=3) == 3   # below capacity: nothing to move, no kernel needed
+
+
+def test_pending_moe_detects_a_later_call_on_the_same_workspace():
+    import torch
+    from tritonllm_b200 import ops
+    ws = torch.zeros(16, dtype=torch.uint8)
+    p = ops.PendingMoe(ws, 1, 64, 64)
+    ops._moe_generation[ws.data_ptr()] = ops._moe_generation.get(ws.data_ptr(), 0) + 1   # what a later expert call does
+    with pytest.raises(RuntimeError, match="overwritten"):
+        ops.moe_combine_add_rmsnorm(p, torch.zeros(1, 64, dtype=torch.bfloat16), torch.ones(64), 1e-5)
+
+
+def test_integration_finds_no_reference_in_an_empty_place(tmp_path, monkeypatch):
+    from tritonllm_b200 import integration
+    monkeypatch.delenv("TRITONLLM_REFERENCE", raising=False)
+    assert integration.reference_path(str(tmp_path)) in (None, integration.reference_path())
+    (tmp_path / "tritonllm").mkdir()
+    assert integration.reference_path(str(tmp_path)) == str(tmp_path)
 
 
 def test_scratch_pool_returns_stable_buffers():

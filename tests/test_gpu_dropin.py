@@ -15,7 +15,7 @@ import oracle as O
 from _util import assert_parity
 
 pytestmark = pytest.mark.gpu
-DEV = "cuda"
+DEV = torch.device("cuda")   # the reference's RotaryEmbedding reads device.type
 
 
 @pytest.fixture(scope="module")

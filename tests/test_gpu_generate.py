@@ -292,3 +292,19 @@ def test_model_from_checkpoint_equals_model_from_tensors(tmp_path, fp4):
     direct.prefill(tokens[:, :8], ca)
     loaded.prefill(tokens[:, :8], cb)
     assert torch.equal(direct.forward_greedy(tokens[:, 8:], ca), loaded.forward_greedy(tokens[:, 8:], cb))
+
+
+def test_generate_raises_when_a_kernel_recorded_a_failure():
+    """A token id outside the vocabulary makes the embedding kernel read row 0 and set the status word; the
+    decode loop must raise instead of yielding tokens computed from it."""
+    ops, G, _lib = _mods()
+    model, _ = _small_model(True)
+    tg = G.TokenGenerator(model, context=32, batch_size=2, use_cuda_graph=False)
+    bad = torch.tensor([[1, 2, 10 ** 6], [3, 4, 5]])
+    with pytest.raises(_lib.B2Error, match="status word"):
+        list(tg.generate(bad, temperature=0.0, max_tokens=2))
+    assert _lib.device_status() == 0   # the check cleared the word
+    good = torch.tensor([[1, 2, 7], [3, 4, 5]])
+    assert len(list(tg.generate(good, temperature=0.0, max_tokens=2))) == 2
+    with pytest.raises(_lib.B2Error):
+        tg.generate_greedy(bad.to("cuda"), 2)

@@ -122,3 +122,29 @@ def test_decode_steps_in_a_cuda_graph(ops):
         assert_parity(O.router_logits(O.rmsnorm(h_ref.reshape(B, 1, 2880), gain2, 1e-5).reshape(B, 2880), wg, bg),
                       outs[1], f"decode step {i}: router logits", max_rel=3e-2, rms_rel=8e-3)
     assert int(offset.item()) == start + 3
+
+
+@pytest.mark.parametrize("world,window", [(8, 0), (2, 128)])
+def test_head_sharded_block_equals_unsharded(ops, world, window):
+    """The optional long-context mode on one GPU: every rank's share (its slice of the QKV weight, its heads'
+    attention) computed in turn, the shares placed side by side as the all-gather would, then the replicated
+    o_proj: equal to the unsharded block bit for bit, and within the bar of the oracle."""
+    from tritonllm_b200 import headshard
+    g = torch.Generator().manual_seed(900 + world)
+    p = _params(g)
+    B, T = 1, 300
+    x = randn(g, B, T, 2880)
+    cos, sin = O.yarn_cos_sin(512)
+    cos_d, sin_d = cos.to(DEV), sin.to(DEV)
+    d = {k: v.to(DEV) for k, v in p.items()}
+    xd = x.to(DEV)
+    parts = []
+    for r in range(world):
+        sh = headshard.shard_attention_weights(d["w_qkv"], d["b_qkv"], d["sinks"], r, world)
+        parts.append(headshard.attention_heads_local(xd, d["norm_gain"], sh, sin_d, cos_d, cos_d.shape[0], 0.125, window).clone())
+    o = torch.cat(parts, dim=1)
+    got = ops.out_residual_forward(o.reshape(B, T, -1), d["w_o"], d["b_o"], xd)
+    want = _block_prefill(ops, x, p, window, cos_d, sin_d, 0)
+    assert torch.equal(got, want)
+    ref, *_ = O.attention_block(x, p, window, cos, sin, 0)
+    assert_parity(ref, got, f"head-sharded block, {world} ranks")

@@ -221,3 +221,24 @@ def test_moe_deferred_combine_with_add_and_norm(T):
     assert h2.data_ptr() == res.data_ptr() and torch.equal(res, h_ref) and torch.equal(y2, y)
     from tritonllm_b200 import _lib
     assert _lib.device_status() == 0
+
+
+def test_moe_flags_an_expert_chosen_twice_by_one_token():
+    """The routing lists count an expert once per token; a duplicate id (never produced by `topk`) is recorded in
+    the device status word instead of silently summing one expert row twice."""
+    ops = _ops()
+    from tritonllm_b200 import _lib
+    gen = torch.Generator().manual_seed(77)
+    T, E, H, I = 4, 8, 256, 128
+    dev = "cuda"
+    x = (torch.randn(T, H, generator=gen)).to(torch.bfloat16).to(dev)
+    w1, w2 = _random_experts(gen, E, 2 * I, H), _random_experts(gen, E, H, I)
+    W1 = ops.ExpertWeightsFp4(ops.ExpertWeights(*(t.to(dev) for t in w1)))
+    W2 = ops.ExpertWeightsFp4(ops.ExpertWeights(*(t.to(dev) for t in w2)))
+    idx = torch.tensor([[0, 1, 2, 3], [1, 1, 4, 5], [0, 2, 4, 6], [1, 3, 5, 7]], dtype=torch.int16, device=dev)
+    vals = torch.full((T, 4), 0.25, device=dev)
+    assert _lib.device_status() == 0
+    ops.moe_experts_decode(x, vals, idx, W1, W2)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0x10
+    assert _lib.device_status() == 0

@@ -27,6 +27,8 @@ PROTOTYPES = {
     "b2_rope_inplace": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _i64, _vp]),
     "b2_qkv_rope_kv_decode": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64,
                                      _i32, _i32, _i32, _i32, _i64, _vp]),
+    "b2_qkv_rope_kv_decode_ragged": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp,
+                                            _i64, _i32, _i64, _i32, _i32, _i32, _i32, _i64, _vp]),
     "b2_oproj_residual_decode": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp]),
     "b2_linear_bias": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp]),
     "b2_qkv_rope_prefill": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32,
@@ -38,6 +40,8 @@ PROTOTYPES = {
     "b2_attn_decode_workspace_bytes": (_sz, [_i64, _i32, _i32]),
     "b2_attn_decode": (_i32, [_vp, _vp, _vp, _vp, _i32, _vp, _i64, _i32, _i32, _i32, _i64, _i64, _i64, _i64, _f32,
                               _i32, _vp, _i32, _vp, _sz, _vp]),
+    "b2_attn_decode_ragged": (_i32, [_vp, _vp, _vp, _vp, _i32, _vp, _i64, _i32, _i32, _i32, _i64, _i64, _i64, _i64, _f32,
+                                     _i32, _vp, _i32, _vp, _i64, _i32, _i64, _vp, _sz, _vp]),
     "b2_attn_decode_static_max_units": (_sz, []),
     "b2_attn_decode_static": (_i32, [_vp, _vp, _vp, _vp, _i32, _vp, _i64, _i32, _i32, _i32, _i64, _i64, _i64, _i64,
                                      _f32, _i32, _vp, _i32, _vp]),

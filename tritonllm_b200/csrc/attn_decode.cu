@@ -54,7 +54,52 @@ struct AttnDecodeArgs {
   int sinks_is_f32, start_q_is_i64, stages;
   long long* trace;  // optional [grid][8] timestamps
   int hg;  // KV heads per CTA tile (<= AD_HG): fewer when the whole problem is small, so more SMs take part
+  // ragged / paged variant only
+  const int32_t* block_table;   // optional [batch][table_stride]: page holding keys page_size*j .. of sequence b
+  long long table_stride;
+  int page_size;                // multiple of AD_TK
 };
+
+constexpr int AD_RAGGED_MAX_BATCH = 2048;   // per-sequence tile counts and positions live in shared memory
+
+// Where a CTA stands in the list of 32-key tiles when sequences have their own lengths: sequence b, head group
+// hgi, tile t of the `tiles` tiles of that sequence.  The list is sequence-major, then head group, then tile;
+// pfx[b] = tiles (of one head group) of the sequences before b.
+struct AdCursor {
+  int b, hgi, t, tiles;
+  __device__ __forceinline__ void seek(long long g, const int* pfx, int batch, int n_hg) {
+    int lo = 0, hi = batch - 1;   // largest b with pfx[b] * n_hg <= g
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (static_cast<long long>(pfx[mid]) * n_hg <= g) lo = mid; else hi = mid - 1;
+    }
+    b = lo;
+    tiles = pfx[b + 1] - pfx[b];
+    const int r = static_cast<int>(g - static_cast<long long>(pfx[b]) * n_hg);
+    hgi = r / tiles;
+    t = r - hgi * tiles;
+  }
+  __device__ __forceinline__ void next(const int* pfx, int batch, int n_hg) {
+    if (++t == tiles) {
+      t = 0;
+      if (++hgi == n_hg) {
+        hgi = 0;
+        if (++b < batch) tiles = pfx[b + 1] - pfx[b];
+      }
+    }
+  }
+};
+// visible key range of a sequence whose new token sits at position sq, and where its first tile starts
+__device__ __forceinline__ void ad_range(long long sq, int n_kv_ctx, int window, int& lo, int& hi, int& lo_al) {
+  long long h = sq + 1 < n_kv_ctx ? sq + 1 : n_kv_ctx;
+  if (h < 0) h = 0;
+  long long l = window > 0 ? sq - window + 1 : 0;
+  if (l < 0) l = 0;
+  if (l > h) l = h;
+  lo = static_cast<int>(l);
+  hi = static_cast<int>(h);
+  lo_al = lo & ~(AD_TK - 1);
+}
 
 // Shared memory: `stages` x 64 KiB of tiles (1024-byte aligned), then this struct.
 struct __align__(16) AttnDecodeSmem {
@@ -71,6 +116,10 @@ __device__ __forceinline__ float load_sink_log2(const AttnDecodeArgs& a, int hea
   return s * 1.4426950408889634f;
 }
 
+// RAGGED = false: one position for the whole batch (the reference's contract).  RAGGED = true: start_q is an
+// array with one position per sequence and the KV store may be paged; tiles then start at multiples of 32 keys
+// (so that a tile never straddles a page) and keys before the window are masked like keys after the position.
+template <bool RAGGED>
 __global__ void __launch_bounds__(AD_THREADS, 1)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                    const AttnDecodeArgs a) {
@@ -98,22 +147,52 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   overlap_wait();   // everything above ran while the kernel before this one was finishing
 
   // ---- work partition, identical in every CTA ------------------------------------------------
-  const long long sq = a.start_q_is_i64 ? *static_cast<const long long*>(a.start_q)
-                                        : static_cast<long long>(*static_cast<const int*>(a.start_q));
-  long long hi_ll = sq + 1 < a.n_kv_ctx ? sq + 1 : a.n_kv_ctx;
-  if (hi_ll < 0) hi_ll = 0;
-  long long lo_ll = a.window > 0 ? sq - a.window + 1 : 0;
-  if (lo_ll < 0) lo_ll = 0;
-  if (lo_ll > hi_ll) lo_ll = hi_ll;
-  const int lo = static_cast<int>(lo_ll), hi = static_cast<int>(hi_ll);
-  const int tpu = max(1, (hi - lo + AD_TK - 1) / AD_TK);      // tiles per unit
   const int HGR = a.hg;                                        // heads per group in this launch
   const int n_hg = (a.n_kv_heads + HGR - 1) / HGR;            // head groups per sequence
   const int units = a.batch * n_hg;                           // unit = (sequence, head group)
-  const long long total = static_cast<long long>(units) * tpu;
+  int lo = 0, hi = 0, tpu = 1;                                 // uniform case: the same for every unit
+  long long total;
+  // ragged case: positions and the running tile count of every sequence, after the barriers in shared memory
+  int* s_pfx = reinterpret_cast<int*>(&sm + 1);                // [batch + 1]
+  int* s_pos = s_pfx + (AD_RAGGED_MAX_BATCH + 1);              // [batch], clamped to int
+  if constexpr (RAGGED) {
+    for (int b = tid; b < a.batch; b += AD_THREADS) {
+      long long sq = a.start_q_is_i64 ? static_cast<const long long*>(a.start_q)[b]
+                                      : static_cast<long long>(static_cast<const int*>(a.start_q)[b]);
+      sq = sq < -1 ? -1 : (sq > 0x3fffffff ? 0x3fffffff : sq);
+      int l, h, la;
+      ad_range(sq, a.n_kv_ctx, a.window, l, h, la);
+      s_pos[b] = static_cast<int>(sq);
+      s_pfx[b + 1] = max(1, (h - la + AD_TK - 1) / AD_TK);
+    }
+    __syncthreads();
+    if (warp == 0) {   // inclusive scan, 32 sequences at a time
+      int carry = 0;
+      for (int base = 0; base < a.batch; base += 32) {
+        const int b = base + lane;
+        int v = b < a.batch ? s_pfx[b + 1] : 0;
+        for (int d = 1; d < 32; d <<= 1) {
+          const int up = __shfl_up_sync(0xffffffffu, v, d);
+          if (lane >= d) v += up;
+        }
+        if (b < a.batch) s_pfx[b + 1] = carry + v;
+        carry += __shfl_sync(0xffffffffu, v, 31);
+      }
+      if (lane == 0) s_pfx[0] = 0;
+    }
+    __syncthreads();
+    total = static_cast<long long>(s_pfx[a.batch]) * n_hg;
+  } else {
+    const long long sq = a.start_q_is_i64 ? *static_cast<const long long*>(a.start_q)
+                                          : static_cast<long long>(*static_cast<const int*>(a.start_q));
+    int lo_al;
+    ad_range(sq, a.n_kv_ctx, a.window, lo, hi, lo_al);
+    tpu = max(1, (hi - lo + AD_TK - 1) / AD_TK);      // tiles per unit
+    total = static_cast<long long>(units) * tpu;
+  }
   long long chunk = (total + gridDim.x - 1) / gridDim.x;
   // short units (window layers, short contexts): hand out whole units, so nothing has to be merged
-  if (tpu <= 16) chunk = (chunk + tpu - 1) / tpu * tpu;
+  if (!RAGGED && tpu <= 16) chunk = (chunk + tpu - 1) / tpu * tpu;
   const long long g_begin = min(total, chunk * blockIdx.x);
   const long long g_end = min(total, g_begin + chunk);
   const int n_my = static_cast<int>(g_end - g_begin);
@@ -124,6 +203,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     // ================================ producer ================================
     if (lane == 0) {
       int issued = 0;
+      AdCursor pcur = {0, 0, 0, 1};
       for (int i = 0; i < n_my; ++i) {
         const int s = i % S, round = i / S;
         if (round > 0 && !mbar_wait_bounded(&sm.empty[s], (round - 1) & 1, abort_flag)) {
@@ -132,15 +212,40 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           break;
         }
         const long long g = g_begin + i;
-        const int u = static_cast<int>(g / tpu), t = static_cast<int>(g - static_cast<long long>(u) * tpu);
-        const int b = u / n_hg, h0 = (u - b * n_hg) * HGR;
+        int b, h0, c_key, c_seq;   // sequence, first head, and the copy's coordinates along keys and sequences / pages
+        if constexpr (RAGGED) {
+          if (i == 0) pcur.seek(g, s_pfx, a.batch, n_hg);
+          b = pcur.b;
+          h0 = pcur.hgi * HGR;
+          int l, h, la;
+          ad_range(s_pos[b], a.n_kv_ctx, a.window, l, h, la);
+          const int key0 = la + pcur.t * AD_TK;
+          if (a.block_table) {
+            c_seq = __ldg(a.block_table + static_cast<size_t>(b) * a.table_stride + key0 / a.page_size);
+            c_key = key0 % a.page_size;
+            if (c_seq < 0) {   // an unmapped page: record it and read page 0 (the keys are masked or garbage either way)
+              atomicOr(a.status, B2_DEV_BAD_INDEX);
+              c_seq = 0;
+            }
+          } else {
+            c_seq = b;
+            c_key = key0;
+          }
+          pcur.next(s_pfx, a.batch, n_hg);
+        } else {
+          const int u = static_cast<int>(g / tpu), t = static_cast<int>(g - static_cast<long long>(u) * tpu);
+          b = u / n_hg;
+          h0 = (u - b * n_hg) * HGR;
+          c_seq = b;
+          c_key = lo + t * AD_TK;
+        }
         const int nh = min(HGR, a.n_kv_heads - h0);
         uint8_t* st = tiles + static_cast<size_t>(s) * AD_STAGE_BYTES;
         mbar_arrive_expect_tx(&sm.full[s], static_cast<uint32_t>(nh) * 2 * AD_HEAD_TILE);
         // one copy per head, K then V, back to back: together they read whole 1 KiB token rows
-        for (int h = 0; h < nh; ++h) tma_load_4d(st + h * AD_HEAD_TILE, &tm_k, &sm.full[s], 0, h0 + h, lo + t * AD_TK, b);
+        for (int h = 0; h < nh; ++h) tma_load_4d(st + h * AD_HEAD_TILE, &tm_k, &sm.full[s], 0, h0 + h, c_key, c_seq);
         for (int h = 0; h < nh; ++h)
-          tma_load_4d(st + (AD_HG + h) * AD_HEAD_TILE, &tm_v, &sm.full[s], 0, h0 + h, lo + t * AD_TK, b);
+          tma_load_4d(st + (AD_HG + h) * AD_HEAD_TILE, &tm_v, &sm.full[s], 0, h0 + h, c_key, c_seq);
         issued = i + 1;
       }
       if (*abort_flag) {
@@ -157,10 +262,13 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     const int g8 = lane >> 2, t4 = lane & 3;
     const int G = a.group, HQ = a.n_kv_heads * a.group;
     float m_run = AD_M_INIT, l_run = 0.f;
+    int lo_tile0 = lo;   // first key of the unit's first tile (ragged: lo rounded down to a multiple of 32)
     float o[AD_D / 8][4];
     uint32_t qa[AD_D / 16][2];
     int cur_u = -1, seg_tiles = 0, cur_b = 0, cur_head = 0;
     bool active = false;  // does this warp's head exist in the current unit?
+    AdCursor ccur = {0, 0, 0, 1};
+    long long cur_u_begin = 0;   // ragged: index of the unit's first tile in the global list
 
     auto begin_unit = [&](int u) {
       cur_u = u;
@@ -170,6 +278,13 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 #pragma unroll
       for (int n = 0; n < AD_D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
       cur_b = u / n_hg;
+      if constexpr (RAGGED) {
+        int la;
+        ad_range(s_pos[cur_b], a.n_kv_ctx, a.window, lo, hi, la);
+        tpu = ccur.tiles;
+        cur_u_begin = (static_cast<long long>(s_pfx[cur_b]) * n_hg) + static_cast<long long>(u - cur_b * n_hg) * tpu;
+        lo_tile0 = la;
+      }
       cur_head = (u - cur_b * n_hg) * HGR + warp;
       active = warp < HGR && cur_head < a.n_kv_heads;
       const uint32_t* qrow = reinterpret_cast<const uint32_t*>(
@@ -200,8 +315,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         return;
       }
       // partial slot: 0 when this unit is the first of the CTA's chunk, else 1
-      const int first_u = static_cast<int>(g_begin / tpu);
-      const size_t slot = static_cast<size_t>(blockIdx.x) * 2 + (u == first_u ? 0 : 1);
+      const long long u_begin = RAGGED ? cur_u_begin : static_cast<long long>(u) * tpu;
+      const size_t slot = static_cast<size_t>(blockIdx.x) * 2 + (u_begin <= g_begin ? 0 : 1);
       const size_t prow = slot * AD_SLOT_ROWS + warp * AD_GMAX + g8;
       if (active) {
 #pragma unroll
@@ -214,7 +329,6 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       }
       __threadfence();
       named_bar_sync(1, AD_HG * 32);
-      const long long u_begin = static_cast<long long>(u) * tpu;
       const int c_first = static_cast<int>(u_begin / chunk), c_last = static_cast<int>((u_begin + tpu - 1) / chunk);
       if (tid == 0) {
         const int old = atomicAdd(a.counters + u, 1);
@@ -238,7 +352,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const int c = min(c0 + k, c_last);  // the tail repeats the last part; its weight is zeroed below
-            const size_t sl = static_cast<size_t>(c) * 2 + (static_cast<int>((chunk * c) / tpu) == u ? 0 : 1);
+            // part c is slot 0 of its CTA when this unit is the first of that CTA's chunk
+            const size_t sl = static_cast<size_t>(c) * 2 + (chunk * c >= u_begin ? 0 : 1);
             const size_t pr = sl * AD_SLOT_ROWS + rsub;
             const float2 ml = __ldcg(reinterpret_cast<const float2*>(a.part_ml + pr * 2));
             pm[k] = ml.x;
@@ -285,11 +400,20 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     bool dead = false;
     for (int i = 0; i < n_my; ++i) {
       const long long g = g_begin + i;
-      const int u = static_cast<int>(g / tpu), t = static_cast<int>(g - static_cast<long long>(u) * tpu);
+      int u, t;
+      if constexpr (RAGGED) {
+        if (i == 0) ccur.seek(g, s_pfx, a.batch, n_hg);
+        u = ccur.b * n_hg + ccur.hgi;
+        t = ccur.t;
+      } else {
+        u = static_cast<int>(g / tpu);
+        t = static_cast<int>(g - static_cast<long long>(u) * tpu);
+      }
       if (u != cur_u) {
         if (cur_u >= 0) end_unit();
         begin_unit(u);
       }
+      if constexpr (RAGGED) ccur.next(s_pfx, a.batch, n_hg);
       const int s = i % S;
       // A warp that gave up keeps walking the tile list without touching data, so that the
       // named barriers of end_unit() still see all consumer warps.
@@ -305,7 +429,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       if (dead) continue;
       if (a.trace && tid == 0 && i == 0) a.trace[blockIdx.x * 8 + 1] = global_timer_ns();
       if (active) {
-        const int key0 = lo + t * AD_TK;
+        const int key0 = lo_tile0 + t * AD_TK;
         uint8_t* st = tiles + static_cast<size_t>(s) * AD_STAGE_BYTES;
         const uint32_t kbase = smem_u32(st + warp * AD_HEAD_TILE);
         uint8_t* vtile = st + (AD_HG + warp) * AD_HEAD_TILE;
@@ -345,7 +469,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int key = key0 + 8 * n + 2 * t4 + e;
-            x[2 * n + e] = key < hi ? sacc[n][e] * a.scale_log2 : -CUDART_INF_F;
+            x[2 * n + e] = (key < hi && (!RAGGED || key >= lo)) ? sacc[n][e] * a.scale_log2 : -CUDART_INF_F;
           }
         }
         float mx = fmaxf(fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3])), fmaxf(fmaxf(x[4], x[5]), fmaxf(x[6], x[7])));
@@ -410,16 +534,25 @@ B2_API size_t b2_attn_decode_workspace_bytes(int64_t batch, int n_kv_heads, int 
   return counters + ml + acc;
 }
 
-B2_API int b2_attn_decode(const void* q, const void* k, const void* v, const void* sinks, int sinks_is_f32, void* out,
-                          int64_t batch, int n_kv_heads, int group, int head_dim, int64_t n_kv_ctx,
-                          int64_t kv_stride_b, int64_t kv_stride_n, int64_t kv_stride_h, float sm_scale, int window,
-                          const void* start_q_dev, int start_q_is_i64, void* workspace, size_t workspace_bytes,
-                          void* stream) {
+namespace {
+// Shared launch path.  Uniform: start_q_dev points at ONE position, k/v are [batch, n_kv_ctx, heads, 64] at the given
+// strides.  Ragged: start_q_dev points at `batch` positions; with a block table k/v are a pool of pages
+// [n_pages, page_size, heads, 64] (kv_stride_b = page stride) and n_kv_ctx the capacity of a sequence.
+int attn_decode_launch(const void* q, const void* k, const void* v, const void* sinks, int sinks_is_f32, void* out,
+                       int64_t batch, int n_kv_heads, int group, int head_dim, int64_t n_kv_ctx, int64_t kv_stride_b,
+                       int64_t kv_stride_n, int64_t kv_stride_h, float sm_scale, int window, const void* start_q_dev,
+                       int start_q_is_i64, void* workspace, size_t workspace_bytes, void* stream, bool ragged,
+                       const int32_t* block_table, int64_t table_stride, int page_size, int64_t n_pages) {
   using namespace b2;
   if (!q || !k || !v || !out || !start_q_dev) return B2_ERR_NULL;
   if (batch < 0 || n_kv_heads <= 0 || group <= 0 || n_kv_ctx <= 0 || window < 0) return B2_ERR_SHAPE;
   if (head_dim != AD_D || group > AD_GMAX) return B2_ERR_UNSUPPORTED;
   if (batch * n_kv_heads > 0x3fffffff || n_kv_ctx > 0x3fffffff) return B2_ERR_UNSUPPORTED;
+  if (ragged && batch > AD_RAGGED_MAX_BATCH) return B2_ERR_UNSUPPORTED;
+  if (block_table) {
+    if (page_size <= 0 || n_pages <= 0 || table_stride <= 0 || table_stride * page_size < n_kv_ctx) return B2_ERR_SHAPE;
+    if (page_size % AD_TK != 0) return B2_ERR_UNSUPPORTED;   // a 32-key tile must lie inside one page
+  }
   if (!aligned16(q) || !aligned16(out)) return B2_ERR_ALIGN;
   if (batch == 0) return B2_OK;
   if (!workspace) return B2_ERR_WORKSPACE;
@@ -430,7 +563,8 @@ B2_API int b2_attn_decode(const void* q, const void* k, const void* v, const voi
 
   CUtensorMap tm_k, tm_v;
   const uint64_t dims[4] = {static_cast<uint64_t>(AD_D), static_cast<uint64_t>(n_kv_heads),
-                            static_cast<uint64_t>(n_kv_ctx), static_cast<uint64_t>(batch)};
+                            static_cast<uint64_t>(block_table ? page_size : n_kv_ctx),
+                            static_cast<uint64_t>(block_table ? n_pages : batch)};
   const uint64_t strides[3] = {static_cast<uint64_t>(kv_stride_h) * 2, static_cast<uint64_t>(kv_stride_n) * 2,
                                static_cast<uint64_t>(kv_stride_b) * 2};
   const uint32_t box[4] = {AD_D, 1, AD_TK, 1};
@@ -464,6 +598,9 @@ B2_API int b2_attn_decode(const void* q, const void* k, const void* v, const voi
   a.window = window;
   a.sinks_is_f32 = sinks_is_f32;
   a.start_q_is_i64 = start_q_is_i64;
+  a.block_table = block_table;
+  a.table_stride = table_stride;
+  a.page_size = page_size;
   {
     size_t slots = 0;
     long long* tb = trace_buffer(&slots);
@@ -477,7 +614,7 @@ B2_API int b2_attn_decode(const void* q, const void* k, const void* v, const voi
     const int64_t tiles_per_seq = (max_keys + AD_TK - 1) / AD_TK + 1;
     int hg = AD_HG;
     // (only for windowed layers: their units are handed out whole, so smaller groups cost no merging)
-    while (window > 0 && max_keys <= 512 && hg > 1 &&
+    while (!ragged && window > 0 && max_keys <= 512 && hg > 1 &&
            batch * ((n_kv_heads + hg - 1) / hg) * tiles_per_seq < 2 * static_cast<int64_t>(grid))
       hg >>= 1;
     a.hg = hg;
@@ -485,12 +622,41 @@ B2_API int b2_attn_decode(const void* q, const void* k, const void* v, const voi
   const int stages = tunable(TUNE_ATTN_DECODE_STAGES);
   a.stages = stages < 1 ? 1 : stages > AD_MAX_STAGES ? AD_MAX_STAGES : stages;
 
-  const size_t smem = attn_decode_smem_bytes(a.stages);
-  cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(smem));
-  if (e != cudaSuccess) return static_cast<int>(e);
-  launch_overlapped(attn_decode_kernel, dim3(grid), dim3(AD_THREADS), smem, static_cast<cudaStream_t>(stream), tm_k, tm_v, a);
+  cudaError_t e;
+  if (ragged) {
+    const size_t smem = attn_decode_smem_bytes(a.stages) + (2 * AD_RAGGED_MAX_BATCH + 1) * sizeof(int);
+    e = cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    launch_overlapped(attn_decode_kernel<true>, dim3(grid), dim3(AD_THREADS), smem, static_cast<cudaStream_t>(stream), tm_k, tm_v, a);
+  } else {
+    const size_t smem = attn_decode_smem_bytes(a.stages);
+    e = cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    launch_overlapped(attn_decode_kernel<false>, dim3(grid), dim3(AD_THREADS), smem, static_cast<cudaStream_t>(stream), tm_k, tm_v, a);
+  }
   return launch_status();
+}
+}  // namespace
+
+B2_API int b2_attn_decode(const void* q, const void* k, const void* v, const void* sinks, int sinks_is_f32, void* out,
+                          int64_t batch, int n_kv_heads, int group, int head_dim, int64_t n_kv_ctx,
+                          int64_t kv_stride_b, int64_t kv_stride_n, int64_t kv_stride_h, float sm_scale, int window,
+                          const void* start_q_dev, int start_q_is_i64, void* workspace, size_t workspace_bytes,
+                          void* stream) {
+  return attn_decode_launch(q, k, v, sinks, sinks_is_f32, out, batch, n_kv_heads, group, head_dim, n_kv_ctx, kv_stride_b,
+                            kv_stride_n, kv_stride_h, sm_scale, window, start_q_dev, start_q_is_i64, workspace,
+                            workspace_bytes, stream, false, nullptr, 0, 0, 0);
+}
+
+B2_API int b2_attn_decode_ragged(const void* q, const void* k, const void* v, const void* sinks, int sinks_is_f32, void* out,
+                                 int64_t batch, int n_kv_heads, int group, int head_dim, int64_t n_kv_ctx,
+                                 int64_t kv_stride_b, int64_t kv_stride_n, int64_t kv_stride_h, float sm_scale,
+                                 int window, const void* positions_dev, int positions_are_i64,
+                                 const int32_t* block_table, int64_t table_stride, int page_size, int64_t n_pages,
+                                 void* workspace, size_t workspace_bytes, void* stream) {
+  return attn_decode_launch(q, k, v, sinks, sinks_is_f32, out, batch, n_kv_heads, group, head_dim, n_kv_ctx, kv_stride_b,
+                            kv_stride_n, kv_stride_h, sm_scale, window, positions_dev, positions_are_i64, workspace,
+                            workspace_bytes, stream, true, block_table, table_stride, page_size, n_pages);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -52,6 +52,10 @@ struct SkinnyArgs {
   const float* sin_tab;
   const float* cos_tab;
   const int64_t* offset;
+  int64_t offset_stride;            // 0: one position for the whole batch; 1: offset[b] is sequence b's position
+  const int32_t* block_table;       // optional [batch][table_stride]: page of a paged KV pool that holds tokens
+  int64_t table_stride;             //   page_size * j .. page_size * (j + 1) - 1 of sequence b (the pool is then
+  int page_size;                    //   [pages][page_size][heads][64] and cs_b is the page stride)
   int64_t max_ctx, cache_ctx;
   __nv_bfloat16* q_out;
   __nv_bfloat16* cache_k;
@@ -259,7 +263,8 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     const int e = (warp - 2) * 32 + lane;  // 0..127
     long long offset = 0, pos = 0;
     bool offset_ok = true;
-    if (a.epi == EPI_QKV) {
+    const bool per_seq = a.epi == EPI_QKV && (a.offset_stride != 0 || a.block_table != nullptr);
+    if (a.epi == EPI_QKV && !per_seq) {
       offset = *a.offset;
       offset_ok = offset >= 0 && offset < a.cache_ctx;
       pos = offset % a.max_ctx;
@@ -287,6 +292,25 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       __nv_bfloat16* dst_lo = nullptr;
       __nv_bfloat16* dst_hi = nullptr;
       bool rotate = false;
+      long long kv_row = static_cast<long long>(b) * a.cs_b + offset * a.cs_n;   // element offset of the token's K/V row
+      if (per_seq) {   // this sequence's own position, and its page when the KV store is paged
+        offset = a.offset[static_cast<size_t>(b) * a.offset_stride];
+        offset_ok = offset >= 0 && offset < a.cache_ctx;
+        pos = offset % a.max_ctx;
+        if (pos < 0) pos += a.max_ctx;
+        if (!offset_ok) {
+          if (qd == 0 && tile == 0) atomicOr(a.status, B2_DEV_BAD_INDEX);
+        } else if (a.block_table) {
+          const long long page = a.block_table[static_cast<size_t>(b) * a.table_stride + offset / a.page_size];
+          kv_row = page * a.cs_b + (offset % a.page_size) * a.cs_n;
+          if (page < 0) {
+            offset_ok = false;
+            if (qd == 0 && tile == 0) atomicOr(a.status, B2_DEV_BAD_INDEX);
+          }
+        } else {
+          kv_row = static_cast<long long>(b) * a.cs_b + offset * a.cs_n;
+        }
+      }
       if (a.epi == EPI_QKV) {
         const int head = tile * 2 + (qd >> 3), jj = (qd & 7) * 4;
         rotate = head < a.n_q + a.n_kv;
@@ -307,7 +331,7 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         } else if (offset_ok) {
           const bool is_k = head < a.n_q + a.n_kv;
           const int kvh = is_k ? head - a.n_q : head - a.n_q - a.n_kv;
-          dst_lo = (is_k ? a.cache_k : a.cache_v) + b * a.cs_b + offset * a.cs_n + kvh * a.cs_h + jj;
+          dst_lo = (is_k ? a.cache_k : a.cache_v) + kv_row + kvh * a.cs_h + jj;
         }
         dst_hi = dst_lo ? dst_lo + 32 : nullptr;
       } else {
@@ -589,6 +613,50 @@ B2_API int b2_qkv_rope_kv_decode(const void* hidden, int64_t hidden_stride_b, co
   const auto al8 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 7u) == 0; };
   a.vec_ok = al8(q_out) && al8(cache_k) && al8(cache_v) && al8(bias) && aligned16(sin_tab) && aligned16(cos_tab) &&
              cache_stride_b % 4 == 0 && cache_stride_n % 4 == 0 && cache_stride_h % 4 == 0;
+  return launch_skinny(hidden, hidden_stride_b, weight, a, static_cast<cudaStream_t>(stream));
+}
+
+B2_API int b2_qkv_rope_kv_decode_ragged(const void* hidden, int64_t hidden_stride_b, const void* weight, const void* bias,
+                                        const float* sin_tab, const float* cos_tab, const int64_t* positions_dev,
+                                        void* q_out, void* kv_k, void* kv_v, int64_t kv_stride_b, int64_t kv_stride_n,
+                                        int64_t kv_stride_h, int64_t kv_ctx, const int32_t* block_table,
+                                        int64_t table_stride, int page_size, int64_t batch, int hidden_size,
+                                        int n_q_heads, int n_kv_heads, int head_dim, int64_t max_ctx, void* stream) {
+  using namespace b2;
+  if (batch < 0 || hidden_size <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || max_ctx <= 0 || kv_ctx <= 0)
+    return B2_ERR_SHAPE;
+  if (block_table && (page_size <= 0 || table_stride <= 0 || table_stride * page_size < kv_ctx)) return B2_ERR_SHAPE;
+  if (head_dim != 64 || hidden_size % SK_KB != 0 || batch > 0x7fffffff) return B2_ERR_UNSUPPORTED;
+  if (batch == 0) return B2_OK;
+  if (!hidden || !weight || !bias || !sin_tab || !cos_tab || !positions_dev || !q_out || !kv_k || !kv_v)
+    return B2_ERR_NULL;
+  if (!aligned16(hidden) || !aligned16(weight) || hidden_stride_b % 8 != 0) return B2_ERR_ALIGN;
+  SkinnyArgs a = {};
+  a.epi = EPI_QKV;
+  a.bias = static_cast<const __nv_bfloat16*>(bias);
+  a.batch = static_cast<int>(batch);
+  a.k_in = hidden_size;
+  a.n_out = (n_q_heads + 2 * n_kv_heads) * head_dim;
+  a.sin_tab = sin_tab;
+  a.cos_tab = cos_tab;
+  a.offset = positions_dev;
+  a.offset_stride = 1;
+  a.block_table = block_table;
+  a.table_stride = table_stride;
+  a.page_size = page_size;
+  a.max_ctx = max_ctx;
+  a.cache_ctx = kv_ctx;
+  a.q_out = static_cast<__nv_bfloat16*>(q_out);
+  a.cache_k = static_cast<__nv_bfloat16*>(kv_k);
+  a.cache_v = static_cast<__nv_bfloat16*>(kv_v);
+  a.cs_b = kv_stride_b;
+  a.cs_n = kv_stride_n;
+  a.cs_h = kv_stride_h;
+  a.n_q = n_q_heads;
+  a.n_kv = n_kv_heads;
+  const auto al8 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 7u) == 0; };
+  a.vec_ok = al8(q_out) && al8(kv_k) && al8(kv_v) && al8(bias) && aligned16(sin_tab) && aligned16(cos_tab) &&
+             kv_stride_b % 4 == 0 && kv_stride_n % 4 == 0 && kv_stride_h % 4 == 0;
   return launch_skinny(hidden, hidden_stride_b, weight, a, static_cast<cudaStream_t>(stream));
 }
 

@@ -516,11 +516,11 @@ def moe_combine_add_rmsnorm(pending: PendingMoe, residual, scale, eps, h_out=Non
     """``x.add_(t)`` with t the MoE output (tritonllm/gpt_oss/triton/model.py:816) and the norm that follows
     (model.py:476, 923), fused with the sum over each token's experts that produces t: returns (h, y) like
     ``add_rmsnorm_forward``.  residual [..., hidden] bf16 with pending.tokens rows; h_out may be residual."""
-    _need_cuda(residual, scale)
-    hidden = pending.hidden
     if _moe_generation.get(pending.ws.data_ptr(), 0) != pending.generation:
         raise RuntimeError("the expert outputs of this PendingMoe were overwritten by a later moe_experts_decode call "
                            "of the same size: combine a deferred call before the next one")
+    _need_cuda(residual, scale)
+    hidden = pending.hidden
     assert residual.dtype == _BF16 and residual.shape[-1] == hidden and residual.stride(-1) == 1
     r2 = residual.reshape(-1, hidden)
     assert r2.shape[0] == pending.tokens and scale.dtype == torch.float32 and scale.shape == (hidden,)
