@@ -13,7 +13,9 @@ Differences from the reference, all additive:
   whole batch, model.py:344);
 * all layers share ONE position counter tensor, advanced once per step, instead of one per layer;
 * a prompt is ingested in slices of sequences so that the activations of a slice stay small;
-* the expert GEMMs of a prompt run through the decode-sized kernel in blocks of 2048 tokens.
+* the expert GEMMs of a prompt run through the decode-sized kernel in blocks of 2048 tokens;
+* optionally every sequence has its own position (``Cache(per_sequence=True)``: prompts of different lengths in
+  one batch) and the KV store may be paged (``PagedKVStore``: pages of a shared pool handed out per sequence).
 """
 from __future__ import annotations
 
@@ -60,11 +62,17 @@ class Cache:
     layers; then only its owner advances it.  The sliding behaviour and its two environment switches
     (DENSE_CACHE_SLIDING, DENSE_CACHE_SLIDE_CHUNK) follow model.py:345-351."""
 
-    def __init__(self, batch_size, n_ctx, n_kv_heads, d_head=64, device=None, offset: torch.Tensor | None = None):
+    paged = False
+
+    def __init__(self, batch_size, n_ctx, n_kv_heads, d_head=64, device=None, offset: torch.Tensor | None = None,
+                 per_sequence: bool = False):
         self.k = torch.zeros((batch_size, n_ctx, n_kv_heads, d_head), dtype=torch.bfloat16, device=device)
         self.v = torch.zeros((batch_size, n_ctx, n_kv_heads, d_head), dtype=torch.bfloat16, device=device)
         self.owns_offset = offset is None
-        self.offset = torch.zeros((1,), dtype=torch.long, device=device) if offset is None else offset
+        # one counter for the batch as in the reference, or (per_sequence) one per sequence, shape [batch]
+        n_pos = batch_size if per_sequence else 1
+        self.offset = torch.zeros((n_pos,), dtype=torch.long, device=device) if offset is None else offset
+        self.per_sequence = per_sequence or self.offset.numel() != 1
         self.enable_sliding_window = os.getenv("DENSE_CACHE_SLIDING", "1").strip().lower() not in _OFF
         default_slide_chunk = max(256, min(n_ctx // 8, 4096))
         env = os.getenv("DENSE_CACHE_SLIDE_CHUNK")
@@ -89,6 +97,8 @@ class Cache:
     def slide_window(self, keep_last_n: int | None = None, current: int | None = None) -> int:
         """Drops the oldest entries and keeps the newest ``keep_last_n`` (default: capacity - slide_chunk)
         at the front of the store; returns the new position.  Same arithmetic as model.py:391-424."""
+        if self.per_sequence:
+            raise ValueError("sliding is defined for a store whose sequences share one position")
         if current is None:
             if not self.owns_offset:
                 # the owner of a shared counter has already moved it when the loop reaches this layer
@@ -109,6 +119,78 @@ class Cache:
         return _CacheView(self.k[b0:b1], self.v[b0:b1], self.offset)
 
 
+class PagedKVStore:
+    """KV store of all layers as pools of pages: per layer k, v [n_pages, page_size, kv_heads, d_head] bf16; ONE
+    block table int32 [batch, max_pages] (the page of tokens page_size*j .. of sequence b, -1 = none yet) and ONE
+    position vector int64 [batch] shared by the layers.  Pages are handed out on the host from a free list
+    (``ensure``) and returned with ``release``; the kernels only read the table.  The reference has no paged store
+    (model.py:340-433 is dense): layout and bookkeeping are this library's, the arithmetic on the pages is the
+    decode kernels'."""
+
+    def __init__(self, n_layers, batch_size, n_ctx, n_kv_heads, d_head=64, page_size=64, n_pages=None, device=None):
+        assert page_size % 32 == 0, "a 32-key attention tile must lie inside one page"
+        self.page_size, self.batch_size = page_size, batch_size
+        self.max_pages = -(-n_ctx // page_size)
+        self.capacity = self.max_pages * page_size
+        self.n_pages = n_pages if n_pages is not None else batch_size * self.max_pages
+        self.k = [torch.zeros((self.n_pages, page_size, n_kv_heads, d_head), dtype=torch.bfloat16, device=device)
+                  for _ in range(n_layers)]
+        self.v = [torch.zeros_like(t) for t in self.k]
+        self.block_table = torch.full((batch_size, self.max_pages), -1, dtype=torch.int32, device=device)
+        self.positions = torch.zeros((batch_size,), dtype=torch.long, device=device)
+        self._free = list(range(self.n_pages - 1, -1, -1))
+        self._owned = [[] for _ in range(batch_size)]
+
+    def ensure(self, b: int, n_tokens: int) -> None:
+        """Makes sure sequence b owns pages for its first ``n_tokens`` tokens."""
+        need = -(-n_tokens // self.page_size)
+        if need > self.max_pages:
+            raise ValueError(f"{n_tokens} tokens exceed the capacity of a sequence ({self.capacity})")
+        have = len(self._owned[b])
+        if need <= have:
+            return
+        if need - have > len(self._free):
+            raise RuntimeError("the page pool is exhausted")
+        new = [self._free.pop() for _ in range(need - have)]
+        self._owned[b].extend(new)
+        self.block_table[b, have:need] = torch.tensor(new, dtype=torch.int32, device=self.block_table.device)
+
+    def release(self, b: int) -> None:
+        self._free.extend(reversed(self._owned[b]))
+        self._owned[b] = []
+        self.block_table[b].fill_(-1)
+        self.positions[b] = 0
+
+    def reset(self) -> None:
+        for b in range(self.batch_size):
+            self.release(b)
+
+    def layer(self, li: int) -> "_PagedLayer":
+        return _PagedLayer(self, li)
+
+    def rows_of(self, b: int, n_tokens: int) -> torch.Tensor:
+        """Row index (page * page_size + slot) in the flattened pool of tokens 0 .. n_tokens-1 of sequence b."""
+        pages = self.block_table[b, : -(-n_tokens // self.page_size)].long()
+        return (pages[:, None] * self.page_size + torch.arange(self.page_size, device=pages.device)[None, :]).reshape(-1)[:n_tokens]
+
+
+class _PagedLayer:
+    """One layer of a PagedKVStore, in the role a Cache plays for a dense store."""
+    paged = True
+    per_sequence = True
+    owns_offset = False
+
+    def __init__(self, store: PagedKVStore, li: int):
+        self.store, self.k, self.v = store, store.k[li], store.v[li]
+        self.block_table, self.offset = store.block_table, store.positions
+
+    def write_prompt(self, b: int, k: torch.Tensor, v: torch.Tensor) -> None:
+        """K/V rows [T, heads, d] of a freshly ingested prompt of sequence b into its pages (Cache.extend's role)."""
+        rows = self.store.rows_of(b, k.shape[0])
+        self.k.view(-1, *self.k.shape[2:]).index_copy_(0, rows, k)
+        self.v.view(-1, *self.v.shape[2:]).index_copy_(0, rows, v)
+
+
 def check_device_status(where: str) -> None:
     """Raises B2Error when a kernel of this process has recorded a failure in the per-device status word since the
     last check (a bounded wait that gave up, a token id or expert index out of range): such a kernel carries on
@@ -125,6 +207,8 @@ class _CacheView:
     k: torch.Tensor
     v: torch.Tensor
     offset: torch.Tensor
+    paged = False
+    per_sequence = False
 
 
 @dataclass
@@ -207,11 +291,17 @@ class Transformer:
     def window(self, layer_idx: int) -> int:
         return self.config.sliding_window if layer_idx % 2 == 0 else 0   # model.py:448
 
-    def make_caches(self, batch_size: int, n_ctx: int) -> list:
+    def make_caches(self, batch_size: int, n_ctx: int, per_sequence: bool = False) -> list:
         c = self.config
-        first = Cache(batch_size, n_ctx, c.num_key_value_heads, c.head_dim, device=self.device)
-        return [first] + [Cache(batch_size, n_ctx, c.num_key_value_heads, c.head_dim, device=self.device, offset=first.offset)
+        first = Cache(batch_size, n_ctx, c.num_key_value_heads, c.head_dim, device=self.device, per_sequence=per_sequence)
+        return [first] + [Cache(batch_size, n_ctx, c.num_key_value_heads, c.head_dim, device=self.device, offset=first.offset,
+                                per_sequence=per_sequence)
                           for _ in range(c.num_hidden_layers - 1)]
+
+    def make_paged_store(self, batch_size: int, n_ctx: int, page_size: int = 64, n_pages: int | None = None) -> PagedKVStore:
+        c = self.config
+        return PagedKVStore(c.num_hidden_layers, batch_size, n_ctx, c.num_key_value_heads, c.head_dim, page_size, n_pages,
+                            device=self.device)
 
     # ---- one block -------------------------------------------------------------------------------------
     def _moe(self, n2: torch.Tensor, p: LayerWeights) -> torch.Tensor:
@@ -242,32 +332,43 @@ class Transformer:
             self._zero[key] = z
         return z
 
-    def _blocks(self, x: torch.Tensor, caches, position: torch.Tensor) -> torch.Tensor:
+    def _blocks(self, x: torch.Tensor, caches, position: torch.Tensor, seq_index: int | None = None) -> torch.Tensor:
         """All blocks and the final norm for x [B, T, hidden] at positions position .. position+T-1.  The
         residual add that closes a block (x.add_(t), model.py:816) is fused into the norm that opens the next
         one, and the last one into the final norm."""
         c = self.config
         B, T, H = x.shape
-        decode = T == 1 and caches is not None
+        decode = T == 1 and caches is not None and seq_index is None   # prefill_sequence ingests even a 1-token prompt
         h, delta = x, self._zeros_like(x)
         hbuf, nbuf = torch.empty_like(x), torch.empty_like(x)
         for li, p in enumerate(self.w.layers):
             cache = caches[li] if caches is not None else None
             self._add_norm(h, delta, p.norm1, hbuf, nbuf)
-            if decode:
+            if decode and cache.paged:
+                q = ops.qkv_rope_paged_decode_forward(nbuf, p.wqkv, p.bqkv, self.sin, self.cos, self.max_context_length,
+                                                      cache.k, cache.v, cache.block_table, position, c.num_attention_heads,
+                                                      c.num_key_value_heads, c.head_dim, kv_capacity=cache.store.capacity)
+                att = ops.attention_decode_paged(q.view(B, 1, c.num_key_value_heads, -1, c.head_dim), cache.k, cache.v,
+                                                 cache.block_table, position, p.sinks, self.sm_scale, self.window(li),
+                                                 kv_capacity=cache.store.capacity)
+                h = ops.out_residual_decode_forward(att, p.wo, p.bo, hbuf)
+            elif decode:
+                per_seq = getattr(cache, "per_sequence", False)
                 q = ops.qkv_rope_cache_decode_forward(nbuf, p.wqkv, p.bqkv, self.sin, self.cos, self.max_context_length,
                                                       cache.k, cache.v, position, c.num_attention_heads,
-                                                      c.num_key_value_heads, c.head_dim)
+                                                      c.num_key_value_heads, c.head_dim, per_sequence=per_seq)
                 att = ops.attention_decode(q.view(B, 1, c.num_key_value_heads, -1, c.head_dim), cache.k, cache.v, p.sinks,
-                                           self.sm_scale, self.window(li), position)
+                                           self.sm_scale, self.window(li), position, per_sequence=per_seq)
                 h = ops.out_residual_decode_forward(att, p.wo, p.bo, hbuf)
             else:
+                dense = cache is not None and not cache.paged
                 q, k, v = ops.qkv_rope_prefill(nbuf, p.wqkv, p.bqkv, self.sin, self.cos, self.max_context_length, position,
                                                c.num_attention_heads, c.num_key_value_heads, c.head_dim,
-                                               cache_k=cache.k if cache is not None else None,
-                                               cache_v=cache.v if cache is not None else None)
+                                               cache_k=cache.k if dense else None, cache_v=cache.v if dense else None)
                 att = ops.attention(q.view(B, T, c.num_key_value_heads, -1, c.head_dim), k, v, p.sinks, self.sm_scale,
                                     self.window(li), position)
+                if cache is not None and cache.paged:   # a whole prompt of one sequence, ingested from position 0
+                    cache.write_prompt(seq_index, k[0], v[0])
                 h = ops.out_residual_forward(att, p.wo, p.bo, hbuf, out=hbuf)
             if B * T <= self.FUSED_ROUTER_ROWS and c.num_experts % 32 == 0 and c.experts_per_token <= 4:
                 n2, vals, idx = ops.norm_router_topk(h, p.norm2, self.eps, p.wg, p.bg, c.experts_per_token, y_out=nbuf)
@@ -298,6 +399,10 @@ class Transformer:
         position = caches[0].offset
         if T == 1:
             out = self._blocks(ops.embedding_forward(tokens, self.w.embedding), caches, position)
+            if caches[0].paged:
+                position.add_(1)
+        elif caches[0].per_sequence:
+            raise ValueError("a store with per-sequence positions ingests prompts one sequence at a time: prefill_sequence()")
         else:
             out = torch.empty((B, T, self.config.hidden_size), dtype=torch.bfloat16, device=self.device)
             step = max(1, self.PREFILL_ROWS // T)
@@ -308,6 +413,22 @@ class Transformer:
         for cch in caches:
             if cch.owns_offset:
                 cch.offset.add_(T)
+        return out
+
+    def prefill_sequence(self, tokens: torch.Tensor, caches, b: int) -> torch.Tensor:
+        """Ingests the prompt ``tokens`` [T] of sequence ``b`` alone, from position 0, into a store whose sequences
+        have their own positions (dense ``Cache(per_sequence=True)`` layers or the layers of a ``PagedKVStore``) and sets
+        that sequence's position to T.  Returns the normalised hidden states [1, T, hidden]."""
+        T = tokens.shape[0]
+        zero = self._zero.setdefault("pos0", torch.zeros(1, dtype=torch.int64, device=self.device))
+        if caches[0].paged:
+            caches[0].store.ensure(b, T)
+            views = caches
+        else:
+            assert caches[0].per_sequence
+            views = [_CacheView(cch.k[b:b + 1], cch.v[b:b + 1], zero) for cch in caches]
+        out = self._blocks(ops.embedding_forward(tokens[None, :], self.w.embedding), views, zero, seq_index=b)
+        caches[0].offset[b] = T
         return out
 
     def forward(self, tokens: torch.Tensor, caches=None) -> torch.Tensor:
@@ -335,13 +456,24 @@ class TokenGenerator:
     with prompts of one common length, a KV store of ``context`` tokens per sequence, the one-token step
     captured in CUDA graphs (one returning logits, one returning greedy ids; CUDA_GRAPH=0 turns capture off)."""
 
-    def __init__(self, model: Transformer, context: int, batch_size: int = 1, use_cuda_graph: bool | None = None):
+    def __init__(self, model: Transformer, context: int, batch_size: int = 1, use_cuda_graph: bool | None = None,
+                 per_sequence: bool = False, paged: bool = False, page_size: int = 64, n_pages: int | None = None):
+        """``per_sequence``: every sequence keeps its own position, so ``generate_ragged`` can take prompts of different
+        lengths; ``paged`` (implies per_sequence): the KV store is a PagedKVStore of ``n_pages`` pages of ``page_size``
+        tokens (default: enough for every sequence to reach ``context``)."""
         self.model, self.device, self.batch_size = model, model.device, batch_size
         if use_cuda_graph is None:
             use_cuda_graph = os.getenv("CUDA_GRAPH", "1").strip().lower() not in {"0", "false", "no", "off"}
         self.use_global_cuda_graph = use_cuda_graph
-        self.caches = model.make_caches(batch_size, context)
-        self.enable_dense_cache_sliding = all(cache.can_slide() for cache in self.caches)
+        self.per_sequence = per_sequence or paged
+        self.store = model.make_paged_store(batch_size, context, page_size, n_pages) if paged else None
+        if paged:
+            self.caches = [self.store.layer(li) for li in range(model.config.num_hidden_layers)]
+            for b in range(batch_size):          # the capture steps below write one token per sequence
+                self.store.ensure(b, 1)
+        else:
+            self.caches = model.make_caches(batch_size, context, per_sequence=per_sequence)
+        self.enable_dense_cache_sliding = not self.per_sequence and all(cache.can_slide() for cache in self.caches)
         self.enable_repeat_pattern_stop = os.getenv("DENSE_REPEAT_PATTERN_STOP", "0").strip().lower() not in _OFF
         self.input_token = torch.zeros((batch_size, 1), dtype=torch.int64, device=self.device)
         self._sampling_graph = self._greedy_graph = None
@@ -359,12 +491,19 @@ class TokenGenerator:
             self._sampling_graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self._sampling_graph):
                 self.logits = model.forward(self.input_token, caches=self.caches)[:, 0]
+            self._reset_store()
+
+    def _reset_store(self):
+        if self.store is not None:
+            self.store.reset()
+        else:
             for cache in self.caches:
                 cache.reset()
 
     @property
     def max_model_len(self) -> int:
-        return min(self.model.max_context_length, self.caches[0].k.shape[1])
+        cap = self.store.capacity if self.store is not None else self.caches[0].k.shape[1]
+        return min(self.model.max_context_length, cap)
 
     def sample_next_token(self, logits: torch.Tensor, temperature: float) -> torch.Tensor:
         """logits fp32 [B, vocab] -> ids [B]; Gumbel-max sampling as model.py:1210-1221."""
@@ -513,3 +652,45 @@ class TokenGenerator:
         torch.cuda.synchronize(self.device)
         check_device_status("generate_greedy")
         return out
+
+    @torch.inference_mode()
+    def generate_ragged(self, prompts: list, new_tokens: int, return_first_logits: bool = False):
+        """Greedy generation for prompts of DIFFERENT lengths in one batch (needs ``per_sequence`` or ``paged``):
+        ``prompts`` is a list of ``batch_size`` token lists.  Every prompt is ingested on its own, then all sequences
+        step together, each at its own position.  Returns ids [B, new_tokens]; with ``return_first_logits`` also the
+        fp32 logits [B, vocab] of the first step.  Stops early when the longest sequence fills its store."""
+        if not self.per_sequence:
+            raise ValueError("this generator was built with one position for the whole batch")
+        if len(prompts) != self.batch_size or any(len(p) == 0 for p in prompts):
+            raise ValueError(f"expected {self.batch_size} non-empty prompts")
+        longest = max(len(p) for p in prompts)
+        if longest > self.max_model_len:
+            raise ValueError(f"Prompt is too long: {longest} tokens exceeds max_model_len={self.max_model_len}.")
+        self._reset_store()
+        last = []
+        for b, p in enumerate(prompts):
+            t = torch.as_tensor(p, dtype=torch.int64, device=self.device)
+            if self.store is not None:
+                self.store.ensure(b, min(self.max_model_len, len(p) + new_tokens))
+            if len(p) > 1:
+                self.model.prefill_sequence(t[:-1], self.caches, b)
+            last.append(int(p[-1]))
+        self.input_token.copy_(torch.tensor(last, dtype=torch.int64, device=self.device).view(-1, 1))
+        out = torch.empty((self.batch_size, new_tokens), dtype=torch.int64, device=self.device)
+        first_logits = None
+        n_done = new_tokens
+        for i in range(new_tokens):
+            if longest - 1 + i >= self.max_model_len:
+                n_done = i
+                break
+            if i == 0 and return_first_logits:
+                first_logits = self._step(False).clone()
+                ids = first_logits.argmax(dim=-1)
+            else:
+                ids = self._step(True)
+            self.input_token.copy_(ids.view(-1, 1))
+            out[:, i].copy_(ids)
+        torch.cuda.synchronize(self.device)
+        check_device_status("generate_ragged")
+        out = out[:, :n_done]
+        return (out, first_logits) if return_first_logits else out

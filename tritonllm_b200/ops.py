@@ -91,8 +91,9 @@ def rope_forward(query, key, sin, cos, max_context_length, offset):
 
 # ---------------------------------------------------------------------------- decode
 def qkv_rope_cache_decode_forward(hidden, weight, bias, sin, cos, max_context_length, cache_k, cache_v, offset,
-                                  num_q_heads, num_kv_heads, head_dim, weight_scale=None):
-    """Drop-in for qkv_rope_cache_decode_forward (triton_kernels.py:1109-1255)."""
+                                  num_q_heads, num_kv_heads, head_dim, weight_scale=None, per_sequence=False):
+    """Drop-in for qkv_rope_cache_decode_forward (triton_kernels.py:1109-1255).  Beyond the reference: ``offset``
+    may hold one position per sequence (shape [batch]; ``per_sequence=True`` says so for a batch of one)."""
     if weight_scale is not None:
         raise NotImplementedError("fp8 weights (ATTN_FP8) are not part of the B200 path")
     _need_cuda(hidden, weight, bias, sin, cos, cache_k, cache_v, offset)
@@ -104,7 +105,8 @@ def qkv_rope_cache_decode_forward(hidden, weight, bias, sin, cos, max_context_le
     assert bias.shape == (total_out,)
     assert cache_k.shape == cache_v.shape and cache_k.stride() == cache_v.stride()
     assert cache_k.shape[0] == batch and cache_k.shape[2] == num_kv_heads and cache_k.shape[3] == head_dim
-    assert offset.shape == (1,) and offset.dtype == torch.int64
+    assert offset.dtype == torch.int64 and offset.is_contiguous()
+    assert offset.shape == (1,) or offset.shape == (batch,), "one position for the batch, or one per sequence"
     assert hidden.dtype == _BF16 and weight.dtype == _BF16 and bias.dtype == _BF16 and cache_k.dtype == _BF16
     hidden2 = hidden.reshape(batch, hidden_size)
     if hidden2.stride(-1) != 1:
@@ -113,10 +115,16 @@ def qkv_rope_cache_decode_forward(hidden, weight, bias, sin, cos, max_context_le
     bias = bias if bias.is_contiguous() else bias.contiguous()
     assert cache_k.stride(3) == 1 and sin.is_contiguous() and cos.is_contiguous()
     q = scratch_pool.get((batch, num_q_heads, head_dim), hidden.dtype, hidden.device)
-    _lib.call("b2_qkv_rope_kv_decode", hidden2.data_ptr(), hidden2.stride(0), weight.data_ptr(), bias.data_ptr(),
-              sin.data_ptr(), cos.data_ptr(), offset.data_ptr(), q.data_ptr(), cache_k.data_ptr(), cache_v.data_ptr(),
-              cache_k.stride(0), cache_k.stride(1), cache_k.stride(2), cache_k.shape[1], batch, hidden_size,
-              num_q_heads, num_kv_heads, head_dim, int(max_context_length), _stream())
+    if offset.shape == (1,) and not per_sequence:   # the reference's contract: the whole batch sits at one position
+        _lib.call("b2_qkv_rope_kv_decode", hidden2.data_ptr(), hidden2.stride(0), weight.data_ptr(), bias.data_ptr(),
+                  sin.data_ptr(), cos.data_ptr(), offset.data_ptr(), q.data_ptr(), cache_k.data_ptr(), cache_v.data_ptr(),
+                  cache_k.stride(0), cache_k.stride(1), cache_k.stride(2), cache_k.shape[1], batch, hidden_size,
+                  num_q_heads, num_kv_heads, head_dim, int(max_context_length), _stream())
+    else:
+        _lib.call("b2_qkv_rope_kv_decode_ragged", hidden2.data_ptr(), hidden2.stride(0), weight.data_ptr(), bias.data_ptr(),
+                  sin.data_ptr(), cos.data_ptr(), offset.data_ptr(), q.data_ptr(), cache_k.data_ptr(), cache_v.data_ptr(),
+                  cache_k.stride(0), cache_k.stride(1), cache_k.stride(2), cache_k.shape[1], 0, 0, 0, batch, hidden_size,
+                  num_q_heads, num_kv_heads, head_dim, int(max_context_length), _stream())
     return q.reshape(batch, 1, num_q_heads * head_dim)
 
 
@@ -156,16 +164,18 @@ def _attn_decode_workspace(batch: int, n_kv_heads: int, group: int, device: torc
     return ws
 
 
-def attention_decode(q, k, v, sinks, sm_scale, sliding_window, start_q):
-    """Drop-in for attention_decode (tritonllm/gpt_oss/triton/attention_tt_decode.py:291-410)."""
+def attention_decode(q, k, v, sinks, sm_scale, sliding_window, start_q, per_sequence=False):
+    """Drop-in for attention_decode (tritonllm/gpt_oss/triton/attention_tt_decode.py:291-410).  Beyond the
+    reference: ``start_q`` may hold one position per sequence (length B; ``per_sequence=True`` says so for B = 1)."""
     _need_cuda(q, k, v, start_q)
-    assert len(start_q) == 1
     bs, n_ctx, n_kv_heads, repeat_kv, head_dim = q.shape
+    assert len(start_q) == 1 or len(start_q) == bs, "one position for the batch, or one per sequence"
+    ragged = per_sequence or len(start_q) != 1
     bs_k, n_kv_ctx, n_kv_heads_k, head_dim_k = k.shape
     assert v.shape == k.shape and v.stride() == k.stride()
     assert n_ctx == 1 and bs == bs_k and n_kv_heads == n_kv_heads_k and head_dim == head_dim_k
     assert q.dtype == _BF16 and k.dtype == _BF16 and v.dtype == _BF16
-    assert k.stride(3) == 1
+    assert k.stride(3) == 1 and start_q.is_contiguous()
     q2 = q.reshape(bs, n_kv_heads * repeat_kv * head_dim)
     if not q2.is_contiguous():
         q2 = q2.contiguous()
@@ -178,10 +188,81 @@ def attention_decode(q, k, v, sinks, sm_scale, sliding_window, start_q):
     assert start_q.dtype in (torch.int32, torch.int64)
     o = scratch_pool.get((bs, n_kv_heads, repeat_kv, head_dim), q.dtype, q.device)
     ws = _attn_decode_workspace(bs, n_kv_heads, repeat_kv, q.device)
-    _lib.call("b2_attn_decode", q2.data_ptr(), k.data_ptr(), v.data_ptr(), _ptr(sinks), sinks_f32, o.data_ptr(), bs,
-              n_kv_heads, repeat_kv, head_dim, n_kv_ctx, k.stride(0), k.stride(1), k.stride(2), float(sm_scale),
-              int(sliding_window or 0), start_q.data_ptr(), 1 if start_q.dtype == torch.int64 else 0, ws.data_ptr(),
-              ws.numel(), _stream())
+    if ragged:
+        _lib.call("b2_attn_decode_ragged", q2.data_ptr(), k.data_ptr(), v.data_ptr(), _ptr(sinks), sinks_f32, o.data_ptr(),
+                  bs, n_kv_heads, repeat_kv, head_dim, n_kv_ctx, k.stride(0), k.stride(1), k.stride(2), float(sm_scale),
+                  int(sliding_window or 0), start_q.data_ptr(), 1 if start_q.dtype == torch.int64 else 0, 0, 0, 0, 0,
+                  ws.data_ptr(), ws.numel(), _stream())
+    else:
+        _lib.call("b2_attn_decode", q2.data_ptr(), k.data_ptr(), v.data_ptr(), _ptr(sinks), sinks_f32, o.data_ptr(), bs,
+                  n_kv_heads, repeat_kv, head_dim, n_kv_ctx, k.stride(0), k.stride(1), k.stride(2), float(sm_scale),
+                  int(sliding_window or 0), start_q.data_ptr(), 1 if start_q.dtype == torch.int64 else 0, ws.data_ptr(),
+                  ws.numel(), _stream())
+    return o.view(bs, 1, n_kv_heads * repeat_kv * head_dim)
+
+
+# ------------------------------------------------------------------------ paged KV store (decode)
+def _check_pool(k_pool, v_pool, block_table, positions, batch, kv_capacity):
+    _need_cuda(k_pool, v_pool, block_table, positions)
+    assert k_pool.dtype == _BF16 and v_pool.dtype == _BF16 and k_pool.dim() == 4 and k_pool.stride(3) == 1
+    assert v_pool.shape == k_pool.shape and v_pool.stride() == k_pool.stride()
+    n_pages, page_size = k_pool.shape[0], k_pool.shape[1]
+    assert block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.shape[0] == batch
+    assert block_table.stride(1) == 1
+    assert positions.dtype == torch.int64 and positions.shape == (batch,) and positions.is_contiguous()
+    if kv_capacity is None:
+        kv_capacity = block_table.shape[1] * page_size
+    assert kv_capacity <= block_table.shape[1] * page_size
+    return n_pages, page_size, int(kv_capacity)
+
+
+def qkv_rope_paged_decode_forward(hidden, weight, bias, sin, cos, max_context_length, k_pool, v_pool, block_table,
+                                  positions, num_q_heads, num_kv_heads, head_dim, kv_capacity=None):
+    """``qkv_rope_cache_decode_forward`` for a paged KV store with one position per sequence: k_pool / v_pool
+    [pages, page_size, kv_heads, head_dim] bf16, block_table int32 [batch, max_pages] (page of tokens
+    page_size*j .. of sequence b), positions int64 [batch].  Token positions[b] of sequence b is written to its
+    page; returns q [batch, 1, Hq*D] (pooled).  The reference has no paged store (its Cache is dense,
+    model.py:340-433); the arithmetic is that of triton_kernels.py:1109-1255."""
+    _need_cuda(hidden, weight, bias, sin, cos)
+    batch, num_tokens, hidden_size = hidden.shape
+    assert num_tokens == 1 and weight.shape == ((num_q_heads + 2 * num_kv_heads) * head_dim, hidden_size)
+    assert hidden.dtype == _BF16 and weight.dtype == _BF16 and bias.dtype == _BF16
+    assert k_pool.shape[2] == num_kv_heads and k_pool.shape[3] == head_dim
+    _, page_size, cap = _check_pool(k_pool, v_pool, block_table, positions, batch, kv_capacity)
+    hidden2 = hidden.reshape(batch, hidden_size)
+    if hidden2.stride(-1) != 1:
+        hidden2 = hidden2.contiguous()
+    assert weight.is_contiguous() and bias.is_contiguous() and sin.is_contiguous() and cos.is_contiguous()
+    q = scratch_pool.get((batch, num_q_heads, head_dim), hidden.dtype, hidden.device)
+    _lib.call("b2_qkv_rope_kv_decode_ragged", hidden2.data_ptr(), hidden2.stride(0), weight.data_ptr(), bias.data_ptr(),
+              sin.data_ptr(), cos.data_ptr(), positions.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
+              k_pool.stride(0), k_pool.stride(1), k_pool.stride(2), cap, block_table.data_ptr(), block_table.stride(0),
+              page_size, batch, hidden_size, num_q_heads, num_kv_heads, head_dim, int(max_context_length), _stream())
+    return q.reshape(batch, 1, num_q_heads * head_dim)
+
+
+def attention_decode_paged(q, k_pool, v_pool, block_table, positions, sinks, sm_scale, sliding_window, kv_capacity=None):
+    """``attention_decode`` over a paged KV store with one position per sequence (see
+    ``qkv_rope_paged_decode_forward`` for the layout): q [B, 1, Hkv, G, D]; returns [B, 1, Hkv*G*D] (pooled).
+    page_size must be a multiple of 32."""
+    _need_cuda(q)
+    bs, n_ctx, n_kv_heads, repeat_kv, head_dim = q.shape
+    assert n_ctx == 1 and q.dtype == _BF16 and k_pool.shape[2] == n_kv_heads and k_pool.shape[3] == head_dim
+    n_pages, page_size, cap = _check_pool(k_pool, v_pool, block_table, positions, bs, kv_capacity)
+    q2 = q.reshape(bs, n_kv_heads * repeat_kv * head_dim)
+    if not q2.is_contiguous():
+        q2 = q2.contiguous()
+    sinks_f32 = 0
+    if sinks is not None:
+        _need_cuda(sinks)
+        assert sinks.numel() == n_kv_heads * repeat_kv and sinks.is_contiguous() and sinks.dtype in (_BF16, torch.float32)
+        sinks_f32 = 1 if sinks.dtype == torch.float32 else 0
+    o = scratch_pool.get((bs, n_kv_heads, repeat_kv, head_dim), q.dtype, q.device)
+    ws = _attn_decode_workspace(bs, n_kv_heads, repeat_kv, q.device)
+    _lib.call("b2_attn_decode_ragged", q2.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), _ptr(sinks), sinks_f32,
+              o.data_ptr(), bs, n_kv_heads, repeat_kv, head_dim, cap, k_pool.stride(0), k_pool.stride(1), k_pool.stride(2),
+              float(sm_scale), int(sliding_window or 0), positions.data_ptr(), 1, block_table.data_ptr(),
+              block_table.stride(0), page_size, n_pages, ws.data_ptr(), ws.numel(), _stream())
     return o.view(bs, 1, n_kv_heads * repeat_kv * head_dim)
 
 
