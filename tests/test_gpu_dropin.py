@@ -86,6 +86,9 @@ def test_attention_block_forward_through_patch(ref, layer):
     ref_outs, ref_err = None, None
     _unpatch(M, originals)
     try:
+        # the first call of the reference's autotuned in-place o_proj kernel runs it once per candidate configuration
+        # on the same residual buffer, so that call's output is not the function of its inputs: warm the tuner up first
+        _run_attention(M, blk, x0, xd, B, ctx)
         ref_outs, ref_cache = _run_attention(M, blk, x0, xd, B, ctx)
     except Exception as exc:  # the reference's own kernels failed on this box
         ref_err = repr(exc)[:300]
@@ -118,10 +121,16 @@ def test_attention_block_forward_through_patch(ref, layer):
     assert_parity(cv[:, : T + 3], cache.v[:, : T + 3], "KV store rows written through the module (v)")
     assert torch.count_nonzero(cache.k[:, T + 3:]) == 0
 
-    # (b) the reference's own kernels on this GPU
+    # (b) the reference's own kernels on this GPU.  Its decode GEMVs multiply and pre-sum in bf16
+    # (triton_kernels.py:787-788, 966-967, 1328), so the reference itself sits a bf16 step or two from exact
+    # arithmetic: the distance between the two implementations may reach the sum of both distances to the oracle
+    # (bar doubled), and this library must be at least as close to the oracle as the reference is.
     if ref_outs is not None:
-        for i, (r, got) in enumerate(zip(ref_outs, outs)):
-            assert_parity(r, got, f"patched AttentionBlock layer {layer}, call {i}, vs the reference's Triton kernels")
+        for i, (r, got, exact) in enumerate(zip(ref_outs, outs, o_ref)):
+            assert_parity(r, got, f"patched AttentionBlock layer {layer}, call {i}, vs the reference's Triton kernels",
+                          max_rel=4e-2, rms_rel=8e-3)
+            ours, theirs = O.rel_err_stats(exact, got.cpu()), O.rel_err_stats(exact, r.cpu())
+            assert ours[1] <= theirs[1] * 1.25 + 5e-4, f"call {i}: rms distance to the oracle {ours[1]:.2e} vs the reference's {theirs[1]:.2e}"
         assert_parity(ref_cache.k[:, : T + 3], cache.k[:, : T + 3], "KV store vs the reference's kernels")
 
 

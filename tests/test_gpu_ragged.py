@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import oracle as O
-from _util import assert_parity, bf16_ulp_diff, randn
+from _util import assert_parity, randn
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -64,7 +64,8 @@ def test_attention_decode_with_per_sequence_positions(ops, B, ctx, window, posit
     # the same sequence alone through the reference-shaped entry point (one position for the batch)
     for b in range(min(B, 5)):
         alone = ops.attention_decode(qd[b:b + 1], kd[b:b + 1], vd[b:b + 1], sd, 0.125, window, pd[b:b + 1].clone()).clone()
-        assert int(bf16_ulp_diff(alone, got[b:b + 1]).max()) <= 2, "ragged batch vs sequence alone"
+        # (not bit for bit: the split points of the key range, and with them the merge order, depend on the batch)
+        assert_parity(alone, got[b:b + 1], "ragged batch vs sequence alone", max_rel=1e-2, rms_rel=2e-3)
     # paged store: the same tiles and the same split points, other addresses -> bit for bit
     for page_size in (32, 64):
         kp, vp, table = _paged_copy(g, torch.nan_to_num(k, nan=7.0), torch.nan_to_num(v, nan=7.0), page_size)

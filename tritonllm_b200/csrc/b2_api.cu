@@ -29,6 +29,7 @@ static void init_tunables() {
     g_tunables[TUNE_MOE_FP4_STAGES] = 0;  // 0: chosen from the token-tile size
     g_tunables[TUNE_MOE_FP4_TOK] = 0;      // 32 / 64: tokens of an expert per CTA (0: 32)
     g_tunables[TUNE_UNEMBED_STAGES] = 0;   // ring depth of the unembedding kernel (0: as deep as shared memory allows)
+    g_tunables[TUNE_MOE_PREFETCH] = 6;     // k-blocks of expert weights requested into L2 ahead of the shared-memory ring (0: off)
     g_tunables[TUNE_LAUNCH_OVERLAP] = 0;   // 1: decode kernels are launched with programmatic stream serialization
     g_tunables[TUNE_TMA_L2_PROMOTION] = 0;  // 0 none, 1 = 64 B, 2 = 128 B, 3 = 256 B
   }
@@ -190,7 +191,7 @@ B2_API int b2_set_tunable(const char* name, int value) {
   if (!name) return B2_ERR_NULL;
   b2::init_tunables();
   static const char* names[b2::TUNE_COUNT] = {"attn_decode_ctas_per_sm", "gemv_ksplit_qkv", "gemv_ksplit_out",
-                                                  "tma_l2_promotion", "attn_decode_stages", "gemm_pair", "moe_fp4_stages", "launch_overlap", "moe_fp4_tok", "unembed_stages"};
+                                                  "tma_l2_promotion", "attn_decode_stages", "gemm_pair", "moe_fp4_stages", "launch_overlap", "moe_fp4_tok", "unembed_stages", "moe_prefetch"};
   for (int i = 0; i < b2::TUNE_COUNT; ++i) {
     if (std::strcmp(name, names[i]) == 0) {
       b2::g_tunables[i] = value;

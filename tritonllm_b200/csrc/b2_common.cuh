@@ -30,7 +30,7 @@ int sm_count();
 int tunable(int id);
 // Optional per-CTA timestamp buffer (8 x int64 per CTA) set with b2_set_trace_buffer; NULL when tracing is off.
 long long* trace_buffer(size_t* slots);
-enum Tunable { TUNE_ATTN_DECODE_CTAS_PER_SM = 0, TUNE_GEMV_KSPLIT_QKV, TUNE_GEMV_KSPLIT_OUT, TUNE_TMA_L2_PROMOTION, TUNE_ATTN_DECODE_STAGES, TUNE_GEMM_PAIR, TUNE_MOE_FP4_STAGES, TUNE_LAUNCH_OVERLAP, TUNE_MOE_FP4_TOK, TUNE_UNEMBED_STAGES, TUNE_COUNT };
+enum Tunable { TUNE_ATTN_DECODE_CTAS_PER_SM = 0, TUNE_GEMV_KSPLIT_QKV, TUNE_GEMV_KSPLIT_OUT, TUNE_TMA_L2_PROMOTION, TUNE_ATTN_DECODE_STAGES, TUNE_GEMM_PAIR, TUNE_MOE_FP4_STAGES, TUNE_LAUNCH_OVERLAP, TUNE_MOE_FP4_TOK, TUNE_UNEMBED_STAGES, TUNE_MOE_PREFETCH, TUNE_COUNT };
 
 // Encodes a tiled tensor map for a bf16 tensor of up to 5 dims (dim 0 innermost, stride 1).
 // strides_bytes[i] is the byte stride of dim i+1.  Returns a B2 status.
@@ -194,6 +194,20 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uin
       "[%2];" ::"r"(smem_u32(dst)),
       "l"(m), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
+}
+// Asks for a tile to be brought from HBM into L2 without a destination in shared memory: a producer that issues
+// these several pipeline steps ahead keeps many more HBM bytes in flight than its ring of shared-memory stages
+// holds, and the later copy into shared memory finds the tile in L2.
+__device__ __forceinline__ void tma_prefetch_l2_4d(const CUtensorMap* m, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(m), "r"(c0), "r"(c1),
+               "r"(c2), "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* m, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(m), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gsrc, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gsrc), "r"(bytes) : "memory");
 }
 // Untiled bulk copies (addresses 16-byte aligned, size a multiple of 16 bytes).
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {

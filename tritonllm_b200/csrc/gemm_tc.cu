@@ -17,41 +17,9 @@
 //                EPI_ROUTER   round to bf16, + fp32 bias                -> fp32 logits [M, N]
 // Every mbarrier wait is bounded; a wait that gives up sets the device status word and the CTA
 // drains, frees its tensor memory and returns.
-#include "tc_common.cuh"
+#include "gemm_tc.cuh"
 
 namespace b2 {
-
-constexpr int GT_BM = 128;
-constexpr int GT_BK = 64;
-constexpr int GT_EPI_WARPS = 8;                     // two per tensor-memory lane quadrant, alternating 64-column chunks
-constexpr int GT_THREADS = 64 + 32 * GT_EPI_WARPS;
-constexpr int GT_A_BYTES = GT_BM * GT_BK * 2;  // 16 KiB
-enum { EPI_PLAIN = 0, EPI_QKV_ROPE = 1, EPI_RESIDUAL = 2, EPI_ROUTER = 3 };
-
-struct GemmArgs {
-  int M, N, K, tiles_m, tiles_n, stages;
-  int vec_ok;  // outputs/bias/residual are 16-byte aligned with leading dimensions that are multiples of 8
-  const __nv_bfloat16* bias;
-  const float* bias_f32;
-  __nv_bfloat16* out;
-  int64_t ld_out;
-  const __nv_bfloat16* residual;
-  int64_t ld_res;
-  float* out_f32;
-  int64_t ld_out_f32;
-  // EPI_QKV_ROPE
-  const float* sin_tab;
-  const float* cos_tab;
-  const int64_t* offset;
-  int64_t max_ctx;
-  int tokens, n_q, n_kv, kv_add_offset, round_before_rope;
-  __nv_bfloat16* q_out;
-  __nv_bfloat16* k_out;
-  __nv_bfloat16* v_out;
-  int64_t kv_sb, kv_sn, kv_sh, kv_ctx;
-  int* status;
-  long long* trace;  // optional [CTA][8] (b2_set_trace_buffer): start ns, end ns, start clock, end clock
-};
 
 constexpr int GT_STAGING_BYTES = GT_EPI_WARPS * 32 * 128;  // one 32 x 64 bf16 block per epilogue warp
 
@@ -301,6 +269,78 @@ __device__ __forceinline__ void epilogue_warp64(const GemmArgs& a, int m0, int l
   __syncwarp();  // the block is out before the next chunk overwrites the staging rows
 }
 
+// ------------------------------------------------------------------------------- MoE (grouped) epilogues
+__device__ __forceinline__ float swiglu_clamped(float g, float l, float alpha, float limit) {
+  g = fminf(g, limit);
+  l = fmaxf(fminf(l, limit), -limit);
+  const float s = __fdividef(g, 1.0f + __expf(-alpha * g));
+  return fmaf(s, l, s);
+}
+// Columns n..n+63 of the 32 rows m0..m0+31 of one expert's output (rows >= m_end belong to the next expert or do not
+// exist and are dropped), written through the warp's staging block so that every store covers whole rows.
+//   EPI_MOE_SWIGLU: column pairs (2j, 2j+1) = (gate, linear) -> 32 outputs per row at columns n/2..n/2+31
+//   EPI_MOE_GATE:   (acc + bias) * gate[row] -> 64 outputs per row
+template <int EPI>
+__device__ __forceinline__ void epilogue_moe64(const GemmArgs& a, int m0, int lane, int n, const float (&lo)[32],
+                                               const float (&hi)[32], int m_end, int expert, uint4* stage) {
+  const int m = m0 + lane;
+  const bool valid = m < m_end;
+  const float4* bias = reinterpret_cast<const float4*>(a.g_bias + static_cast<size_t>(expert) * a.N + n);
+  uint4* my_row = stage + lane * 8;
+  const int sw = lane & 7;
+  __nv_bfloat16* dst = nullptr;
+  if (EPI == EPI_MOE_SWIGLU) {
+    if (valid) {
+      dst = a.out + static_cast<size_t>(m) * a.ld_out + (n >> 1);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {   // outputs 8g..8g+7 from columns 16g..16g+15
+        const float(&v)[32] = g < 2 ? lo : hi;
+        const int e0 = 16 * (g & 1);
+        float r[8];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float4 b4 = __ldg(bias + 4 * g + q);
+          r[2 * q] = swiglu_clamped(v[e0 + 4 * q] + b4.x, v[e0 + 4 * q + 1] + b4.y, a.alpha, a.limit);
+          r[2 * q + 1] = swiglu_clamped(v[e0 + 4 * q + 2] + b4.z, v[e0 + 4 * q + 3] + b4.w, a.alpha, a.limit);
+        }
+        my_row[g ^ sw] = make_uint4(pack_bf16(r[0], r[1]), pack_bf16(r[2], r[3]), pack_bf16(r[4], r[5]), pack_bf16(r[6], r[7]));
+      }
+    }
+    __syncwarp();
+    const unsigned long long mine = reinterpret_cast<unsigned long long>(dst);
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {   // 8 rows x 64 bytes per instruction
+      const int r = 8 * it + (lane >> 2), c = lane & 3;
+      const unsigned long long row_dst = __shfl_sync(0xffffffffu, mine, r);
+      if (row_dst) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(row_dst) + 8 * c) = stage[r * 8 + (c ^ (r & 7))];
+    }
+  } else {
+    if (valid) {
+      dst = a.out + static_cast<size_t>(m) * a.ld_out + n;
+      const float gate = __ldg(a.g_gate + m);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const float(&v)[32] = c < 4 ? lo : hi;
+        const int e = 8 * (c & 3);
+        const float4 b0 = __ldg(bias + 2 * c), b1 = __ldg(bias + 2 * c + 1);
+        my_row[c ^ sw] = make_uint4(pack_bf16((v[e + 0] + b0.x) * gate, (v[e + 1] + b0.y) * gate),
+                                    pack_bf16((v[e + 2] + b0.z) * gate, (v[e + 3] + b0.w) * gate),
+                                    pack_bf16((v[e + 4] + b1.x) * gate, (v[e + 5] + b1.y) * gate),
+                                    pack_bf16((v[e + 6] + b1.z) * gate, (v[e + 7] + b1.w) * gate));
+      }
+    }
+    __syncwarp();
+    const unsigned long long mine = reinterpret_cast<unsigned long long>(dst);
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int r = 4 * it + (lane >> 3), c = lane & 7;
+      const unsigned long long row_dst = __shfl_sync(0xffffffffu, mine, r);
+      if (row_dst) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(row_dst) + 8 * c) = stage[r * 8 + (c ^ (r & 7))];
+    }
+  }
+  __syncwarp();  // the block is out before the next chunk overwrites the staging rows
+}
+
 // ---------------------------------------------------------------------------------------------- kernel
 template <int BN, int EPI>
 __global__ void __launch_bounds__(GT_THREADS, 1)
@@ -497,7 +537,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int S = a.stages;
   const int nkb = (a.K + KSUB * GT_BK - 1) / (KSUB * GT_BK);  // stages per tile; TMA zero-fills k beyond K
-  const int n_tiles = a.tiles_m * a.tiles_n;           // 256-row tiles
+  constexpr bool GROUPED = EPI == EPI_MOE_SWIGLU || EPI == EPI_MOE_GATE;   // tiles come from a device-side list
+  const int n_tiles = (GROUPED ? __ldg(a.g_n_tiles) : a.tiles_m) * a.tiles_n;   // 256-row tiles
   const uint32_t rank = cluster_cta_rank();            // 0: leader, 1: peer
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   volatile int* abort_flag = &bar.abort_flag;
@@ -533,8 +574,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     int it = 0, issued = 0;
     bool ok = true;
     for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
-      const int m0 = (tile / a.tiles_n) * (2 * GT_BM) + static_cast<int>(rank) * GT_BM;
-      const int n0 = (tile % a.tiles_n) * BN + static_cast<int>(rank) * HALF_N;
+      int m0 = (tile / a.tiles_n) * (2 * GT_BM) + static_cast<int>(rank) * GT_BM;
+      int n0 = (tile % a.tiles_n) * BN + static_cast<int>(rank) * HALF_N;
+      if (GROUPED) {   // rows of the tile's expert (a tile may run past them: those rows are computed and dropped), its weights
+        const int mt = tile / a.tiles_n;
+        m0 = __ldg(a.g_tile_row0 + mt) + static_cast<int>(rank) * GT_BM;
+        n0 += __ldg(a.g_tile_expert + mt) * a.N;
+      }
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const int s = it % S, round = it / S;
         if (round > 0 &&
@@ -633,15 +679,25 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       if (dead) break;
       const long long e1 = a.trace ? clock64() : 0;
       tc_fence_after_sync();
-      const int m = (tile / a.tiles_n) * (2 * GT_BM) + static_cast<int>(rank) * GT_BM + lane_grp * 32 + lane;
+      int m = (tile / a.tiles_n) * (2 * GT_BM) + static_cast<int>(rank) * GT_BM + lane_grp * 32 + lane;
       const int n0 = (tile % a.tiles_n) * BN;
+      int m_end = 0, expert = 0;
+      if (GROUPED) {
+        const int mt = tile / a.tiles_n, row0 = __ldg(a.g_tile_row0 + mt);
+        m = row0 + static_cast<int>(rank) * GT_BM + lane_grp * 32 + lane;
+        m_end = row0 + __ldg(a.g_tile_rows + mt);
+        expert = __ldg(a.g_tile_expert + mt);
+      }
       const uint32_t trow = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + buf * BN;
 #pragma unroll 1
       for (int c = 64 * ((warp - 2) >> 2); c < BN; c += 64 * (GT_EPI_WARPS / 4)) {
         float lo[32], hi[32];
         tmem_ld_32x32(trow + c, lo);
         tmem_ld_32x32(trow + c + 32, hi);
-        epilogue_warp64<EPI>(a, m - lane, lane, n0 + c, lo, hi, offset, stage);
+        if constexpr (GROUPED)
+          epilogue_moe64<EPI>(a, m - lane, lane, n0 + c, lo, hi, m_end, expert, stage);
+        else
+          epilogue_warp64<EPI>(a, m - lane, lane, n0 + c, lo, hi, offset, stage);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -755,6 +811,65 @@ static int launch_gemm_tc_pair(const void* a_ptr, int64_t lda, const void* w_ptr
   if (e != cudaSuccess) return static_cast<int>(e);
   *launched = true;
   return launch_status();
+}
+
+template <int EPI>
+static int launch_moe_grouped_t(const void* a_ptr, int64_t lda, const void* w_ptr, int64_t ldw, GemmArgs g, int max_tiles,
+                                cudaStream_t stream) {
+  constexpr int BN = 192, KSUB = 2;
+  constexpr int STAGE_BYTES = KSUB * (GT_A_BYTES + (BN / 2) * GT_BK * 2);
+  CUtensorMap tm_a, tm_w;
+  const uint64_t dims_a[2] = {static_cast<uint64_t>(g.K), static_cast<uint64_t>(g.M)};
+  const uint64_t dims_w[2] = {static_cast<uint64_t>(g.K), static_cast<uint64_t>(g.tiles_m) * g.N};   // tiles_m carries the expert count in
+  const uint64_t str_a[1] = {static_cast<uint64_t>(lda) * 2}, str_w[1] = {static_cast<uint64_t>(ldw) * 2};
+  const uint32_t box_a[2] = {GT_BK, GT_BM}, box_w[2] = {GT_BK, BN / 2};
+  int rc = make_tensor_map_bf16(&tm_a, a_ptr, 2, dims_a, str_a, box_a, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != B2_OK) return rc;
+  rc = make_tensor_map_bf16(&tm_w, w_ptr, 2, dims_w, str_w, box_w, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != B2_OK) return rc;
+  g.tiles_m = 0;   // the tile list lives on the device
+  g.tiles_n = g.N / BN;
+  int stages = (225 * 1024 - GT_STAGING_BYTES) / STAGE_BYTES;
+  g.stages = stages > 8 ? 8 : stages;
+  g.status = device_status_ptr();
+  if (!g.status) return B2_ERR_DRIVER;
+  g.trace = nullptr;
+  const size_t smem = static_cast<size_t>(g.stages) * STAGE_BYTES + sizeof(GemmBarriers) + GT_STAGING_BYTES + 1024;
+  cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<BN, EPI, KSUB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.gridDim = dim3(2 * sm_count(), 1, 1);
+  cfg.blockDim = dim3(GT_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n_clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&n_clusters, gemm_tc_pair_kernel<BN, EPI, KSUB>, &cfg) != cudaSuccess || n_clusters < 1) {
+    (void)cudaGetLastError();
+    return B2_ERR_UNSUPPORTED;
+  }
+  const long long upper = static_cast<long long>(max_tiles) * g.tiles_n;   // the list can hold at most this many tiles
+  const int pairs = static_cast<int>(upper < n_clusters ? (upper < 1 ? 1 : upper) : n_clusters);
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<BN, EPI, KSUB>, tm_a, tm_w, g);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return launch_status();
+}
+
+// g.tiles_m carries the number of experts in (the rows of w_ptr are experts * g.N)
+int launch_moe_grouped_gemm(int epi, const void* a_ptr, int64_t lda, const void* w_ptr, int64_t ldw, GemmArgs g, int max_tiles,
+                            cudaStream_t stream) {
+  if (g.N % 192 != 0 || g.K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0) return B2_ERR_UNSUPPORTED;
+  if (epi == EPI_MOE_SWIGLU) return launch_moe_grouped_t<EPI_MOE_SWIGLU>(a_ptr, lda, w_ptr, ldw, g, max_tiles, stream);
+  if (epi == EPI_MOE_GATE) return launch_moe_grouped_t<EPI_MOE_GATE>(a_ptr, lda, w_ptr, ldw, g, max_tiles, stream);
+  return B2_ERR_UNSUPPORTED;
 }
 
 // Large problems go to the pair kernel (tunable "gemm_pair"), everything else to one CTA per tile.

@@ -500,6 +500,33 @@ __device__ __forceinline__ uint32_t moe_block_scale_byte(float amax) {
   return static_cast<uint32_t>(eb < 1 ? 1 : (eb > 253 ? 253 : eb));
 }
 
+// Eight consecutive values of a row -> their two block-scaled E4M3 terms.  The four threads of an aligned quad hold the
+// 32 elements of one scale group (the whole warp must call this together): qb[term] = the 8 codes, sbyte[term] = the
+// group's E8M0 scale byte.
+__device__ __forceinline__ void moe_quant8(float (&v)[8], uint32_t (&qb)[2][2], uint32_t (&sbyte)[2]) {
+#pragma unroll
+  for (int term = 0; term < 2; ++term) {
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const uint32_t sb = moe_block_scale_byte(amax);
+    const float inv = __uint_as_float((254u - sb) << 23), sc = __uint_as_float(sb << 23);
+    uint16_t q[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      q[i] = f32x2_to_e4m3x2(v[2 * i] * inv, v[2 * i + 1] * inv);
+      const float2 d = e4m3x2_to_f32x2(q[i]);
+      v[2 * i] -= d.x * sc;       // exact: what the first term could not hold
+      v[2 * i + 1] -= d.y * sc;
+    }
+    qb[term][0] = q[0] | (static_cast<uint32_t>(q[1]) << 16);
+    qb[term][1] = q[2] | (static_cast<uint32_t>(q[3]) << 16);
+    sbyte[term] = sb;
+  }
+}
+
 // One CTA per row; a thread owns 8 consecutive elements, four threads one 32-element group.  With `meta` the CTA is
 // a routed (token, slot) pair: it reads the token's row and writes the row of the expert-sorted order (the gather).
 __global__ void __launch_bounds__(128) moe_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, int K,
@@ -530,27 +557,7 @@ __global__ void __launch_bounds__(128) moe_quant_kernel(const __nv_bfloat16* __r
     }
     uint32_t qb[2][2];
     uint32_t sbyte[2];
-#pragma unroll
-    for (int term = 0; term < 2; ++term) {
-      float amax = 0.f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-      const uint32_t sb = moe_block_scale_byte(amax);
-      const float inv = __uint_as_float((254u - sb) << 23), sc = __uint_as_float(sb << 23);
-      uint16_t q[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        q[i] = f32x2_to_e4m3x2(v[2 * i] * inv, v[2 * i + 1] * inv);
-        const float2 d = e4m3x2_to_f32x2(q[i]);
-        v[2 * i] -= d.x * sc;       // exact: what the first term could not hold
-        v[2 * i + 1] -= d.y * sc;
-      }
-      qb[term][0] = q[0] | (static_cast<uint32_t>(q[1]) << 16);
-      qb[term][1] = q[2] | (static_cast<uint32_t>(q[3]) << 16);
-      sbyte[term] = sb;
-    }
+    moe_quant8(v, qb, sbyte);
     if (live) {
       *reinterpret_cast<uint2*>(q_hi + static_cast<size_t>(row) * K + 8 * c) = make_uint2(qb[0][0], qb[0][1]);
       *reinterpret_cast<uint2*>(q_lo + static_cast<size_t>(row) * K + 8 * c) = make_uint2(qb[1][0], qb[1][1]);
@@ -581,6 +588,13 @@ struct MoeFp4Args {
   const MoeMeta* meta;
   __nv_bfloat16* out;
   int N, nkb, tiles, bn_max, stages, sf_col;
+  // SwiGLU epilogue: the activations leave the kernel already split into the two E4M3 terms the second GEMM reads
+  uint8_t* q2_hi;           // [rows][K2]
+  uint8_t* q2_lo;
+  uint8_t* sf2_hi;          // [rows][sf2_stride]
+  uint8_t* sf2_lo;
+  int K2, sf2_stride;
+  int prefetch;             // k-blocks of weights (codes + scale block) requested into L2 ahead of the ring
   int tok;                  // tokens of one expert per CTA (32 or 64); the rest go to the next CTAs along grid.x
   float alpha, limit;
   int* status;
@@ -653,8 +667,18 @@ moe_expert_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     const int xblocks = bn >> 5;
     const uint8_t* sfa_g = a.sfa + (static_cast<size_t>(e) * a.tiles + tile) * nkb * 512;
     bool ok = true;
+    const int PF = a.prefetch;
+    if (leader)
+      for (int kb = 0; kb < PF && kb < nkb; ++kb) {
+        tma_prefetch_l2_4d(&tm_w, kb * FP4_KB, tile * MOE_FT, e, 0);
+        bulk_prefetch_l2(sfa_g + static_cast<size_t>(kb) * 512, 512);
+      }
     for (int kb = 0; kb < nkb && ok; ++kb) {
       const int s = kb % S, round = kb / S;
+      if (leader && PF > 0 && kb + PF < nkb) {   // before the wait: the request leaves as early as possible
+        tma_prefetch_l2_4d(&tm_w, (kb + PF) * FP4_KB, tile * MOE_FT, e, 0);
+        bulk_prefetch_l2(sfa_g + static_cast<size_t>(kb + PF) * 512, 512);
+      }
       if (round > 0) ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar.empty[s], (round - 1) & 1, abort_flag));
       if (!ok) break;
       if (leader) {
@@ -783,12 +807,51 @@ moe_expert_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     asm volatile("bar.sync 1, 128;" ::: "memory");
     constexpr int PIECES = OUT_F / 8;
     const int out_n = EPI == MOE_EPI_SWIGLU ? a.N / 2 : a.N;
-    for (int it = t4; it < n_e * PIECES; it += 128) {
-      const int tok = it / PIECES, pc = it - tok * PIECES;
-      const int col = tile * OUT_F + pc * 8;
-      if (col + 8 <= out_n)
-        *reinterpret_cast<uint4*>(a.out + static_cast<size_t>(row0 + tok) * out_n + col) =
-            *reinterpret_cast<const uint4*>(dump + tok * OUT_F + pc * 8);
+    if constexpr (EPI == MOE_EPI_SWIGLU) {
+      // the bf16 activations go straight into the form the second GEMM reads: two block-scaled E4M3 terms per row, one
+      // scale byte per 32 features (a tile's 64 features are two whole groups); a thread owns 8 features, a quad a group
+      const int total = n_e * PIECES;
+      for (int base = 0; base < total; base += 128) {   // uniform trip count: the shuffles need whole warps
+        const int it = base + t4;
+        const bool live = it < total;
+        const int tok = live ? it / PIECES : 0, pc = it - (it / PIECES) * PIECES;
+        float v[8];
+        if (live) {
+          const uint4 p = *reinterpret_cast<const uint4*>(dump + tok * OUT_F + pc * 8);
+          v[0] = bf16lo(p.x); v[1] = bf16hi(p.x); v[2] = bf16lo(p.y); v[3] = bf16hi(p.y);
+          v[4] = bf16lo(p.z); v[5] = bf16hi(p.z); v[6] = bf16lo(p.w); v[7] = bf16hi(p.w);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = 0.f;
+        }
+        uint32_t qb[2][2];
+        uint32_t sbyte[2];
+        moe_quant8(v, qb, sbyte);
+        const int col = tile * OUT_F + pc * 8;
+        if (live && col + 8 <= out_n) {
+          const size_t row = static_cast<size_t>(row0 + tok);
+          *reinterpret_cast<uint2*>(a.q2_hi + row * a.K2 + col) = make_uint2(qb[0][0], qb[0][1]);
+          *reinterpret_cast<uint2*>(a.q2_lo + row * a.K2 + col) = make_uint2(qb[1][0], qb[1][1]);
+          if ((pc & 3) == 0) {
+            const int g = col >> 5;
+            a.sf2_hi[row * a.sf2_stride + g] = static_cast<uint8_t>(sbyte[0]);
+            a.sf2_lo[row * a.sf2_stride + g] = static_cast<uint8_t>(sbyte[1]);
+            if (g == a.K2 / 32 - 1)   // groups past K2 (the weights are zero there) get a harmless scale of 1
+              for (int gg = g + 1; gg < a.sf2_stride; ++gg) {
+                a.sf2_hi[row * a.sf2_stride + gg] = 127;
+                a.sf2_lo[row * a.sf2_stride + gg] = 127;
+              }
+          }
+        }
+      }
+    } else {
+      for (int it = t4; it < n_e * PIECES; it += 128) {
+        const int tok = it / PIECES, pc = it - tok * PIECES;
+        const int col = tile * OUT_F + pc * 8;
+        if (col + 8 <= out_n)
+          *reinterpret_cast<uint4*>(a.out + static_cast<size_t>(row0 + tok) * out_n + col) =
+              *reinterpret_cast<const uint4*>(dump + tok * OUT_F + pc * 8);
+      }
     }
   }
   tc_fence_before_sync();
@@ -1015,8 +1078,13 @@ B2_API int b2_moe_experts_decode_fp4(const void* x, int64_t ldx, const int16_t* 
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   MoeMeta* meta = reinterpret_cast<MoeMeta*>(ws);
   ws += moe_align(sizeof(MoeMeta));
-  ws += moe_align(static_cast<size_t>(rows) * hidden * 2);   // (the conversion path's gathered rows: unused here)
-  __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(ws);
+  // the conversion path's regions for the gathered rows and the bf16 activations hold, here, the second GEMM's input as
+  // the SwiGLU epilogue writes it: scale bytes of the two terms, then the two terms' codes
+  uint8_t* sf2_hi = ws;
+  uint8_t* sf2_lo = ws + moe_align(static_cast<size_t>(rows) * sf_stride_max);
+  ws += moe_align(static_cast<size_t>(rows) * hidden * 2);
+  uint8_t* q2_hi = ws;
+  uint8_t* q2_lo = ws + static_cast<size_t>(rows) * intermediate;
   ws += moe_align(static_cast<size_t>(rows) * intermediate * 2);
   __nv_bfloat16* ybuf = reinterpret_cast<__nv_bfloat16*>(ws);
   ws += moe_align(static_cast<size_t>(rows) * hidden * 2);
@@ -1050,8 +1118,9 @@ B2_API int b2_moe_experts_decode_fp4(const void* x, int64_t ldx, const int16_t* 
     // the rows of this stage as two block-scaled E4M3 terms; the first stage gathers the tokens' rows on the way
     if (stage == 0)
       launch_overlapped(moe_quant_kernel, dim3(rows), dim3(128), 0, st, static_cast<const __nv_bfloat16*>(x), ldx, K, q_hi, q_lo, sf_hi, sf_lo, 4 * nkb, meta);
-    else
-      launch_overlapped(moe_quant_kernel, dim3(rows), dim3(128), 0, st, act, K, K, q_hi, q_lo, sf_hi, sf_lo, 4 * nkb, nullptr);
+    // (the second GEMM's rows were quantised by the first GEMM's epilogue)
+    const uint8_t* in_hi = stage == 0 ? q_hi : q2_hi;
+    const uint8_t* in_lo = stage == 0 ? q_lo : q2_lo;
     CUtensorMap tm_w, tm_hi, tm_lo;
     const uint64_t wd[4] = {static_cast<uint64_t>(Kp), static_cast<uint64_t>(N), static_cast<uint64_t>(n_experts), 1};
     const uint64_t wstr[3] = {static_cast<uint64_t>(Kp / 2), static_cast<uint64_t>(N) * (Kp / 2),
@@ -1063,17 +1132,23 @@ B2_API int b2_moe_experts_decode_fp4(const void* x, int64_t ldx, const int16_t* 
     const uint64_t xd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(rows)};
     const uint64_t xstr[1] = {static_cast<uint64_t>(K)};
     const uint32_t xbox[2] = {FP4_KB, 32};
-    rc = make_tensor_map(&tm_hi, CU_TENSOR_MAP_DATA_TYPE_UINT8, q_hi, 2, xd, xstr, xbox, CU_TENSOR_MAP_SWIZZLE_128B);
+    rc = make_tensor_map(&tm_hi, CU_TENSOR_MAP_DATA_TYPE_UINT8, in_hi, 2, xd, xstr, xbox, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != B2_OK) return rc;
-    rc = make_tensor_map(&tm_lo, CU_TENSOR_MAP_DATA_TYPE_UINT8, q_lo, 2, xd, xstr, xbox, CU_TENSOR_MAP_SWIZZLE_128B);
+    rc = make_tensor_map(&tm_lo, CU_TENSOR_MAP_DATA_TYPE_UINT8, in_lo, 2, xd, xstr, xbox, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != B2_OK) return rc;
     MoeFp4Args a;
     a.sfa = static_cast<const uint8_t*>(stage == 0 ? w1_sf : w2_sf);
-    a.sf_hi = sf_hi;
-    a.sf_lo = sf_lo;
+    a.sf_hi = stage == 0 ? sf_hi : sf2_hi;
+    a.sf_lo = stage == 0 ? sf_lo : sf2_lo;
     a.bias = stage == 0 ? b1 : b2_;
     a.meta = meta;
-    a.out = stage == 0 ? act : ybuf;
+    a.out = stage == 0 ? nullptr : ybuf;
+    a.q2_hi = q2_hi;
+    a.q2_lo = q2_lo;
+    a.sf2_hi = sf2_hi;
+    a.sf2_lo = sf2_lo;
+    a.K2 = intermediate;
+    a.sf2_stride = 4 * ((intermediate + FP4_KB - 1) / FP4_KB);
     a.N = N;
     a.nkb = nkb;
     a.tiles = (N + MOE_FT - 1) / MOE_FT;
@@ -1081,6 +1156,7 @@ B2_API int b2_moe_experts_decode_fp4(const void* x, int64_t ldx, const int16_t* 
     a.stages = stages;
     a.sf_col = 2 * bn_max;
     a.tok = tok;
+    a.prefetch = tunable(TUNE_MOE_PREFETCH) < 0 ? 0 : (tunable(TUNE_MOE_PREFETCH) > 32 ? 32 : tunable(TUNE_MOE_PREFETCH));
     a.alpha = alpha;
     a.limit = limit;
     a.status = status;
