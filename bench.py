@@ -294,6 +294,7 @@ KERNEL_CASES = [
     ("f1 MoE expert MLP, 32 tokens (routing + quantise + 2 GEMMs + combine)", "moe_decode", dict(batch=32), "hbm"),
     ("f1 MoE expert MLP, 256 tokens", "moe_decode", dict(batch=256), "hbm"),
     ("f1 MoE expert MLP, 2048 tokens (prompt-sized)", "moe_decode", dict(batch=2048), "tensor"),
+    ("f1 MoE expert MLP, 8192 tokens (MXFP4 -> bf16 expansion + grouped GEMMs)", "moe_prefill", dict(batch=8192, copies=1), "tensor"),
     ("f2 unembedding + arg-max (32 seq)", "unembed", dict(batch=32), "hbm"),
     ("f2 unembedding + arg-max (256 seq)", "unembed", dict(batch=256), "hbm"),
 ]

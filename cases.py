@@ -10,7 +10,7 @@ would land in the window).  Prints one JSON line: algorithmic bytes per call, me
 microseconds per call, GB/s and the fraction of the measured HBM copy bandwidth.
 
 Cases: attn_decode, rmsnorm, add_rmsnorm, rope, swiglu, topk, qkv_decode, oproj_decode,
-mxfp4, moe_decode, router_fused, unembed, decode_stack, generate, qkv_prefill, oproj_prefill, router, attn_prefill (the last four are tensor-bound: TFLOP/s is reported too).
+mxfp4, moe_decode, moe_prefill, router_fused, unembed, decode_stack, generate, qkv_prefill, oproj_prefill, router, attn_prefill (the last four are tensor-bound: TFLOP/s is reported too).
 """
 from __future__ import annotations
 
@@ -195,6 +195,20 @@ def build_case(name: str, a):
                 return expert_fn(x, rw1, rw1s, rw2, rw2s, b1, b2, rdata, gi, si)
             return ref_moe, nbytes, f"T={T} E={E} touched={touched} hidden=2880 (reference routing + matmul_ogs)"
         return (lambda: ops.moe_experts_decode(x, vals, idx, w1, w2)), nbytes, f"T={T} E={E} touched={touched} hidden=2880 fp4={not a.no_fp4}"
+    if name == "moe_prefill":   # prompt-sized MoE: MXFP4 -> bf16 expansion of all experts + grouped tensor-core GEMMs
+        T, E = a.batch, (a.moe_experts or 32)
+        H = I = 2880
+        x = _bf(T, H)
+        vals, idx, _ = ops.topk(torch.randn(T, E, device=dev), 4)
+        def w(n, k):
+            return ops.ExpertWeightsFp4(ops.ExpertWeights(torch.randint(0, 256, (E, n, k // 2), dtype=torch.uint8, device=dev),
+                                                          torch.randint(118, 124, (E, n, k // 32), dtype=torch.uint8, device=dev),
+                                                          torch.randn(E, n, device=dev) * 0.1))
+        w1, w2 = w(2 * I, H), w(H, I)
+        per_expert = (2 * I) * (H // 2 + H // 32 + 4) + H * (I // 2 + I // 32 + 4)
+        nbytes = E * per_expert + T * H * 2 * 2
+        return (lambda: ops.moe_experts_prefill(x, vals, idx, w1, w2)), nbytes, f"T={T} E={E} hidden=2880 (grouped bf16 GEMM)", \
+            2.0 * T * 4 * (2 * I * H + H * I)
     if name == "attn_prefill":
         B, T, W = a.batch, a.ctx, a.window
         q = _bf(B, T, 8, 8, 64)

@@ -301,6 +301,27 @@ int b2_moe_combine_add_rmsnorm(const void* workspace, size_t workspace_bytes, in
                                int intermediate, const void* residual, int64_t residual_stride, const float* gain,
                                float eps, void* h_out, int64_t h_stride, void* y_out, int64_t y_stride, void* stream);
 
+/* ---- MoE expert MLP, prompt-sized batches ------------------------------------
+ * The same computation as b2_moe_experts_decode_fp4 for thousands of tokens at once: the tokens routed to an
+ * expert are the M rows of a grouped GEMM (256-row tiles on CTA pairs, tcgen05, bf16), so the work is tensor-bound
+ * instead of re-streaming every weight tile per 32 tokens.  Replaces moe_experts (gpt_oss/triton/moe.py:54-87):
+ * routing metadata (triton_kernels/routing.py:93-166, 208-289: per-expert offsets and the tile map ExptData
+ * carries), matmul_ogs with gather and the fused SwiGLU, matmul_ogs with gammas, and the scatter-sum of
+ * _finalize_matmul (triton_kernels/matmul_ogs_details/_p_matmul_ogs.py:113-495, _finalize_matmul.py:189-378).
+ * Weights are bf16 [experts * N, K] row-major: b2_moe_upcast_packed expands the packed MXFP4 layout of the
+ * decode-sized path (codes [E][N][Kp/2] with K padded to a multiple of 128, scale blocks
+ * [E][ceil(N/128)][Kp/128][512]) into it, exactly.  x [T, hidden] bf16, topk_idx int16 [T,4] (8-byte aligned),
+ * topk_w fp32 [T,4] as b2_topk_softmax returns them, b1 fp32 [E][2*intermediate], b2 fp32 [E][hidden] (16-byte
+ * aligned), out [T, hidden] bf16.  hidden % 192 == 0 and (2*intermediate) % 192 == 0.  An expert index out of
+ * range, or the same expert twice for one token, is dropped and recorded as B2_DEV_BAD_INDEX. */
+size_t b2_moe_prefill_workspace_bytes(int64_t tokens, int n_experts, int hidden, int intermediate);
+int b2_moe_upcast_packed(const void* codes, const void* scale_blocks, void* out_bf16, int n_experts, int n, int k,
+                         void* stream);
+int b2_moe_experts_prefill(const void* x, int64_t ldx, const int16_t* topk_idx, const float* topk_w, const void* w1_bf16,
+                           const float* b1, const void* w2_bf16, const float* b2, void* out, int64_t ld_out,
+                           void* workspace, size_t workspace_bytes, int64_t tokens, int n_experts, int hidden,
+                           int intermediate, float alpha, float limit, void* stream);
+
 /* ---- Unembedding for decode: logits and greedy token ---------------------------------
  * logits[b, v] = sum_k hidden[b, k] * weight[v, k] (fp32 accumulation), stored as bf16 when `logits` is
  * given; token_ids[b] (int64, optional) = arg-max over v of the fp32 sums, the smallest v on ties,

@@ -242,3 +242,102 @@ def test_moe_flags_an_expert_chosen_twice_by_one_token():
     torch.cuda.synchronize()
     assert _lib.device_status() == 0x10
     assert _lib.device_status() == 0
+
+
+# ----------------------------------------------------------------------------- prompt-sized batches (grouped GEMM)
+def _packed(w):
+    ops = _ops()
+    dev = "cuda"
+    return ops.ExpertWeightsFp4(ops.ExpertWeights(w[0].to(dev), w[1].to(dev), w[2].to(dev)))
+
+
+@pytest.mark.parametrize("E,N,K", [(3, 320, 384), (2, 5760, 2880), (5, 192, 96)])
+def test_upcast_of_the_packed_layout_is_exact(E, N, K):
+    """b2_moe_upcast_packed reads the padded codes and the 512-byte scale blocks of ExpertWeightsFp4 and must give
+    exactly the values the reference's upcast gives for the original tensors."""
+    from tritonllm_b200 import _lib
+    gen = torch.Generator().manual_seed(E * 1000 + N)
+    w = _random_experts(gen, E, N, K, scale_lo=100, scale_hi=140)
+    pk = _packed(w)
+    out = torch.empty((E * N, K), dtype=torch.bfloat16, device="cuda")
+    _lib.call("b2_moe_upcast_packed", pk.codes.data_ptr(), pk.sf.data_ptr(), out.data_ptr(), E, N, K,
+              torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    want = torch.from_numpy(O.mxfp4_upcast(w[0].reshape(E * N, K // 2).numpy(), w[1].reshape(E * N, K // 32).numpy()))
+    assert torch.equal(out.cpu().float(), want.float())
+
+
+def _routing(gen, T, E):
+    logits = torch.randn(T, E, generator=gen)
+    vals, idx = O.topk_softmax(logits, 4)[:2]
+    return vals, idx.to(torch.int16)
+
+
+@pytest.mark.parametrize("T,E,H,I", [(700, 8, 384, 192), (2049, 32, 384, 192), (300, 4, 768, 384)])
+def test_moe_prefill_vs_oracle_small_dims(T, E, H, I):
+    ops = _ops()
+    gen = torch.Generator().manual_seed(T + E)
+    x = torch.randn(T, H, generator=gen).to(torch.bfloat16)
+    vals, idx = _routing(gen, T, E)
+    w1, w2 = _random_experts(gen, E, 2 * I, H), _random_experts(gen, E, H, I)
+    out = ops.moe_experts_prefill(x.cuda(), vals.cuda(), idx.cuda(), _packed(w1), _packed(w2))
+    torch.cuda.synchronize()
+    from tritonllm_b200 import _lib
+    assert _lib.device_status() == 0
+    assert_parity(_oracle(x, vals, idx, w1, w2), out, f"prompt-sized MoE T={T} E={E}")
+
+
+def test_moe_prefill_real_dims_against_the_oracle_and_the_decode_sized_kernel():
+    ops = _ops()
+    gen = torch.Generator().manual_seed(4242)
+    T, E, H, I = 3000, 32, 2880, 2880
+    x = torch.randn(T, H, generator=gen).to(torch.bfloat16)
+    vals, idx = _routing(gen, T, E)
+    idx[100:140] = torch.tensor([0, 1, 2, 3], dtype=torch.int16)      # a run of tokens on the same experts
+    w1, w2 = _random_experts(gen, E, 2 * I, H), _random_experts(gen, E, H, I, scale_lo=113, scale_hi=118)
+    W1, W2 = _packed(w1), _packed(w2)
+    xd, vd, idd = x.cuda(), vals.cuda(), idx.cuda()
+    out = ops.moe_experts_prefill(xd, vd, idd, W1, W2)
+    small = torch.cat([ops.moe_experts_decode(xd[r:r + 1500], vd[r:r + 1500], idd[r:r + 1500], W1, W2) for r in (0, 1500)])
+    torch.cuda.synchronize()
+    from tritonllm_b200 import _lib
+    assert _lib.device_status() == 0
+    # both paths multiply exactly and accumulate in fp32: only the order of the sums differs
+    assert_parity(small, out, "grouped GEMM vs decode-sized kernel", rms_rel=1e-3)
+    sel = torch.cat([torch.arange(0, 24), torch.arange(100, 108), torch.arange(T - 8, T)])
+    assert_parity(_oracle(x[sel], vals[sel], idx[sel], w1, w2), out[sel], "prompt-sized MoE, sampled tokens vs oracle")
+
+
+def test_moe_prefill_config4_shape_and_edges():
+    """BASELINE config 4's token count and expert count (16384 tokens, 128 experts, hidden 2880): every token of the
+    grouped-GEMM path against the decode-sized kernel run in blocks, plus experts without tokens."""
+    ops = _ops()
+    gen = torch.Generator().manual_seed(77)
+    T, E, H, I = 16384, 128, 2880, 2880
+    x = torch.randn(T, H, generator=gen).to(torch.bfloat16).cuda()
+    logits = torch.randn(T, E, generator=gen)
+    logits[:, 5] = -1e9           # expert 5 never chosen
+    logits[:, 100:104] -= 50.0    # nor these
+    vals, idx = O.topk_softmax(logits, 4)[:2]
+    vd, idd = vals.cuda(), idx.to(torch.int16).cuda()
+    gd = torch.Generator(device="cuda").manual_seed(78)
+
+    def experts(n, k, lo, hi):
+        w = ops.ExpertWeights(torch.randint(0, 256, (E, n, k // 2), dtype=torch.uint8, device="cuda", generator=gd),
+                              torch.randint(lo, hi, (E, n, k // 32), dtype=torch.uint8, device="cuda", generator=gd),
+                              torch.randn(E, n, device="cuda", generator=gd) * 0.1)
+        return ops.ExpertWeightsFp4(w)
+    W1, W2 = experts(2 * I, H, 118, 124), experts(H, I, 113, 118)
+    out = ops.moe_experts_prefill(x, vd, idd, W1, W2)
+    ref = torch.cat([ops.moe_experts_decode(x[r:r + 2048], vd[r:r + 2048], idd[r:r + 2048], W1, W2) for r in range(0, T, 2048)])
+    torch.cuda.synchronize()
+    from tritonllm_b200 import _lib
+    assert _lib.device_status() == 0
+    assert_parity(ref, out, "config 4 shape: grouped GEMM vs decode-sized kernel", rms_rel=1e-3)
+    assert torch.equal(ops.moe_experts_prefill(x, vd, idd, W1, W2), out)     # deterministic despite the atomic row order
+    bad = idd.clone()
+    bad[7, 2] = 500
+    bad[9, 1] = bad[9, 0]
+    ops.moe_experts_prefill(x, vd, bad, W1, W2)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0x10

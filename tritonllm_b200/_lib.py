@@ -60,6 +60,10 @@ PROTOTYPES = {
                                          _i32, _i32, _f32, _f32, _vp]),
     "b2_moe_experts_decode": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _sz, _i64, _i32,
                                      _i32, _i32, _f32, _f32, _vp]),
+    "b2_moe_prefill_workspace_bytes": (_sz, [_i64, _i32, _i32, _i32]),
+    "b2_moe_upcast_packed": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
+    "b2_moe_experts_prefill": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _sz, _i64, _i32, _i32, _i32,
+                                      _f32, _f32, _vp]),
     "b2_swiglu": (_i32, [_vp, _i64, _vp, _i64, _i64, _i64, _f32, _f32, _vp]),
     "b2_topk_softmax": (_i32, [_vp, _i64, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _i64, _i64, _vp, _i32, _vp]),
 }

@@ -29,7 +29,7 @@ static void init_tunables() {
     g_tunables[TUNE_MOE_FP4_STAGES] = 0;  // 0: chosen from the token-tile size
     g_tunables[TUNE_MOE_FP4_TOK] = 0;      // 32 / 64: tokens of an expert per CTA (0: 32)
     g_tunables[TUNE_UNEMBED_STAGES] = 0;   // ring depth of the unembedding kernel (0: as deep as shared memory allows)
-    g_tunables[TUNE_MOE_PREFETCH] = 6;     // k-blocks of expert weights requested into L2 ahead of the shared-memory ring (0: off)
+    g_tunables[TUNE_MOE_PREFETCH] = 0;     // k-blocks of expert weights requested into L2 ahead of the shared-memory ring (0: off; 3-12 measured no faster)
     g_tunables[TUNE_LAUNCH_OVERLAP] = 0;   // 1: decode kernels are launched with programmatic stream serialization
     g_tunables[TUNE_TMA_L2_PROMOTION] = 0;  // 0 none, 1 = 64 B, 2 = 128 B, 3 = 256 B
   }

@@ -275,23 +275,42 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     // contiguous bytes of each slice's dump and write runs of 64-128 contiguous bytes of the output row;
     // this CTA takes every KS-th group of 128 items
     const int items = bn * 16;
-    for (int it = rank * 128 + e; it < items; it += KS * 128) {
+    // An item's operands (bias, rotation, residual, destination) and then its slices' sums.  Two items are in flight
+    // per thread: the global loads of both are issued before either's remote shared-memory reads, so a thread waits
+    // once per pair instead of once per item (at 256 sequences a thread has about ten items).
+    struct Item {
+      bool live;
+      int c, r_lo, r_hi, n_lo, n_hi;
+      bool rotate;
+      float bias_lo[4], bias_hi[4], cs[4], sn[4], res_lo[4], res_hi[4];
+      __nv_bfloat16* dst_lo;
+      __nv_bfloat16* dst_hi;
+      float4 lo, hi;
+    };
+    auto prep = [&](int it, Item& I) {
+      I.live = false;
+      I.dst_lo = I.dst_hi = nullptr;
+      if (it >= items) return;
       const int c = it >> 4, qd = it & 15;
       const int b = b0 + c;
-      if (b >= a.batch) continue;
-      const int r_lo = a.epi == EPI_QKV ? ((qd >> 3) * 64 + (qd & 7) * 4) : qd * 4;  // RoPE pair (j, j+32) / rows (r, r+64)
-      const int r_hi = a.epi == EPI_QKV ? r_lo + 32 : r_lo + 64;
-      const int f_lo = tile * SK_FT + r_lo, f_hi = tile * SK_FT + r_hi;
-      const int n_lo = min(4, a.n_out - f_lo), n_hi = min(4, a.n_out - f_hi);   // valid features of each quad
-      if (n_lo <= 0) continue;
-      // epilogue operands first, so their latency overlaps the remote shared-memory reads
-      float bias_lo[4], bias_hi[4], cs[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
-      float res_lo[4] = {0.f, 0.f, 0.f, 0.f}, res_hi[4] = {0.f, 0.f, 0.f, 0.f};
-      ld_bf16x4(a.bias + f_lo, a.vec_ok, n_lo, bias_lo);
-      ld_bf16x4(a.bias + f_hi, a.vec_ok, n_hi, bias_hi);
-      __nv_bfloat16* dst_lo = nullptr;
-      __nv_bfloat16* dst_hi = nullptr;
-      bool rotate = false;
+      if (b >= a.batch) return;
+      I.c = c;
+      I.r_lo = a.epi == EPI_QKV ? ((qd >> 3) * 64 + (qd & 7) * 4) : qd * 4;  // RoPE pair (j, j+32) / rows (r, r+64)
+      I.r_hi = a.epi == EPI_QKV ? I.r_lo + 32 : I.r_lo + 64;
+      const int f_lo = tile * SK_FT + I.r_lo, f_hi = tile * SK_FT + I.r_hi;
+      I.n_lo = min(4, a.n_out - f_lo);
+      I.n_hi = min(4, a.n_out - f_hi);   // valid features of each quad
+      if (I.n_lo <= 0) return;
+      I.live = true;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        I.cs[q] = 1.f;
+        I.sn[q] = 0.f;
+        I.res_lo[q] = I.res_hi[q] = 0.f;
+      }
+      ld_bf16x4(a.bias + f_lo, a.vec_ok, I.n_lo, I.bias_lo);
+      ld_bf16x4(a.bias + f_hi, a.vec_ok, I.n_hi, I.bias_hi);
+      I.rotate = false;
       long long kv_row = static_cast<long long>(b) * a.cs_b + offset * a.cs_n;   // element offset of the token's K/V row
       if (per_seq) {   // this sequence's own position, and its page when the KV store is paged
         offset = a.offset[static_cast<size_t>(b) * a.offset_stride];
@@ -313,57 +332,72 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       }
       if (a.epi == EPI_QKV) {
         const int head = tile * 2 + (qd >> 3), jj = (qd & 7) * 4;
-        rotate = head < a.n_q + a.n_kv;
-        if (rotate && a.vec_ok) {
+        I.rotate = head < a.n_q + a.n_kv;
+        if (I.rotate && a.vec_ok) {
           const float4 c4 = __ldg(reinterpret_cast<const float4*>(a.cos_tab + pos * 32 + jj));
           const float4 s4 = __ldg(reinterpret_cast<const float4*>(a.sin_tab + pos * 32 + jj));
-          cs[0] = c4.x; cs[1] = c4.y; cs[2] = c4.z; cs[3] = c4.w;
-          sn[0] = s4.x; sn[1] = s4.y; sn[2] = s4.z; sn[3] = s4.w;
-        } else if (rotate) {
+          I.cs[0] = c4.x; I.cs[1] = c4.y; I.cs[2] = c4.z; I.cs[3] = c4.w;
+          I.sn[0] = s4.x; I.sn[1] = s4.y; I.sn[2] = s4.z; I.sn[3] = s4.w;
+        } else if (I.rotate) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            cs[q] = __ldg(a.cos_tab + pos * 32 + jj + q);
-            sn[q] = __ldg(a.sin_tab + pos * 32 + jj + q);
+            I.cs[q] = __ldg(a.cos_tab + pos * 32 + jj + q);
+            I.sn[q] = __ldg(a.sin_tab + pos * 32 + jj + q);
           }
         }
         if (head < a.n_q) {
-          dst_lo = a.q_out + (static_cast<size_t>(b) * a.n_q + head) * 64 + jj;
+          I.dst_lo = a.q_out + (static_cast<size_t>(b) * a.n_q + head) * 64 + jj;
         } else if (offset_ok) {
           const bool is_k = head < a.n_q + a.n_kv;
           const int kvh = is_k ? head - a.n_q : head - a.n_q - a.n_kv;
-          dst_lo = (is_k ? a.cache_k : a.cache_v) + kv_row + kvh * a.cs_h + jj;
+          I.dst_lo = (is_k ? a.cache_k : a.cache_v) + kv_row + kvh * a.cs_h + jj;
         }
-        dst_hi = dst_lo ? dst_lo + 32 : nullptr;
+        I.dst_hi = I.dst_lo ? I.dst_lo + 32 : nullptr;
       } else {
         __nv_bfloat16* res = a.residual + static_cast<size_t>(b) * a.res_stride;
-        dst_lo = res + f_lo;
-        dst_hi = res + f_hi;
-        ld_bf16x4(dst_lo, a.vec_ok, n_lo, res_lo);
-        ld_bf16x4(dst_hi, a.vec_ok, n_hi, res_hi);
+        I.dst_lo = res + f_lo;
+        I.dst_hi = res + f_hi;
+        ld_bf16x4(I.dst_lo, a.vec_ok, I.n_lo, I.res_lo);
+        ld_bf16x4(I.dst_hi, a.vec_ok, I.n_hi, I.res_hi);
       }
-      float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
-      for (int rr = 0; rr < KS; ++rr) {  // fixed order: deterministic sums
-        const float* remote = cluster.map_shared_rank(dump, rr) + c * SK_TS;
-        const float4 pl = *reinterpret_cast<const float4*>(remote + r_lo);
-        const float4 ph = *reinterpret_cast<const float4*>(remote + r_hi);
-        lo.x += pl.x; lo.y += pl.y; lo.z += pl.z; lo.w += pl.w;
-        hi.x += ph.x; hi.y += ph.y; hi.z += ph.z; hi.w += ph.w;
+    };
+    auto gather = [&](Item& I) {   // the slices' partial sums, fixed order: deterministic
+      I.lo = make_float4(0.f, 0.f, 0.f, 0.f);
+      I.hi = I.lo;
+      if (!I.live) return;
+      for (int rr = 0; rr < KS; ++rr) {
+        const float* remote = cluster.map_shared_rank(dump, rr) + I.c * SK_TS;
+        const float4 pl = *reinterpret_cast<const float4*>(remote + I.r_lo);
+        const float4 ph = *reinterpret_cast<const float4*>(remote + I.r_hi);
+        I.lo.x += pl.x; I.lo.y += pl.y; I.lo.z += pl.z; I.lo.w += pl.w;
+        I.hi.x += ph.x; I.hi.y += ph.y; I.hi.z += ph.z; I.hi.w += ph.w;
       }
-      if (!dst_lo) continue;  // K/V of a position outside the cache: nothing is written
-      float vl[4] = {lo.x + bias_lo[0], lo.y + bias_lo[1], lo.z + bias_lo[2], lo.w + bias_lo[3]};
-      float vh[4] = {hi.x + bias_hi[0], hi.y + bias_hi[1], hi.z + bias_hi[2], hi.w + bias_hi[3]};
+    };
+    auto finish = [&](Item& I) {
+      if (!I.live || !I.dst_lo) return;  // (K/V of a position outside the cache: nothing is written)
+      float vl[4] = {I.lo.x + I.bias_lo[0], I.lo.y + I.bias_lo[1], I.lo.z + I.bias_lo[2], I.lo.w + I.bias_lo[3]};
+      float vh[4] = {I.hi.x + I.bias_hi[0], I.hi.y + I.bias_hi[1], I.hi.z + I.bias_hi[2], I.hi.w + I.bias_hi[3]};
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        if (rotate) {
-          const float rl = vl[q] * cs[q] - vh[q] * sn[q], rh = vh[q] * cs[q] + vl[q] * sn[q];
+        if (I.rotate) {
+          const float rl = vl[q] * I.cs[q] - vh[q] * I.sn[q], rh = vh[q] * I.cs[q] + vl[q] * I.sn[q];
           vl[q] = rl;
           vh[q] = rh;
         }
-        vl[q] += res_lo[q];
-        vh[q] += res_hi[q];
+        vl[q] += I.res_lo[q];
+        vh[q] += I.res_hi[q];
       }
-      st_bf16x4(dst_lo, a.vec_ok, n_lo, vl);
-      st_bf16x4(dst_hi, a.vec_ok, n_hi, vh);
+      st_bf16x4(I.dst_lo, a.vec_ok, I.n_lo, vl);
+      st_bf16x4(I.dst_hi, a.vec_ok, I.n_hi, vh);
+    };
+    for (int it = rank * 128 + e; it < items; it += 2 * KS * 128) {
+      Item A, B;
+      prep(it, A);
+      prep(it + KS * 128, B);
+      gather(A);
+      gather(B);
+      finish(A);
+      finish(B);
     }
   }
   cluster.sync();  // peers may still be reading this CTA's shared memory

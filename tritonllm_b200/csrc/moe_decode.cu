@@ -741,15 +741,27 @@ moe_expert_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       return (n2 < 2 * bn && n < n_e) ? __ldg(reinterpret_cast<const uint32_t*>(sf + static_cast<size_t>(row0 + n) * sf_stride) + kb)
                                      : 0x7f7f7f7fu;
     };
-    uint32_t nx[2] = {load_tsf(t4, 0), load_tsf(t4 + 128, 0)};
+    // the words of the next TSF_AHEAD stages are in registers: a load has that many stages to come back from L2
+    constexpr int TSF_AHEAD = 4;
+    uint32_t nx[TSF_AHEAD][2];
+#pragma unroll
+    for (int d = 0; d < TSF_AHEAD; ++d) {
+      nx[d][0] = d < nkb ? load_tsf(t4, d) : 0x7f7f7f7fu;
+      nx[d][1] = (d < nkb && atoms > 1) ? load_tsf(t4 + 128, d) : 0x7f7f7f7fu;
+    }
     const int off = (t4 & 31) * 16 + (t4 >> 5) * 4;
     bool ok = true;
     for (int kb = 0; kb < nkb; ++kb) {
       const int s = kb % S, round = kb / S;
-      const uint32_t cur[2] = {nx[0], nx[1]};
-      if (kb + 1 < nkb) {
-        nx[0] = load_tsf(t4, kb + 1);
-        if (atoms > 1) nx[1] = load_tsf(t4 + 128, kb + 1);
+      const uint32_t cur[2] = {nx[0][0], nx[0][1]};
+#pragma unroll
+      for (int d = 0; d + 1 < TSF_AHEAD; ++d) {
+        nx[d][0] = nx[d + 1][0];
+        nx[d][1] = nx[d + 1][1];
+      }
+      if (kb + TSF_AHEAD < nkb) {
+        nx[TSF_AHEAD - 1][0] = load_tsf(t4, kb + TSF_AHEAD);
+        if (atoms > 1) nx[TSF_AHEAD - 1][1] = load_tsf(t4 + 128, kb + TSF_AHEAD);
       }
       if (round > 0) ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar.empty[s], (round - 1) & 1, abort_flag));
       if (!ok) break;

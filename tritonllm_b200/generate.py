@@ -273,7 +273,7 @@ class ModelWeights:
 class Transformer:
     """Inference forward of the whole model (Transformer, model.py:886-936)."""
 
-    PREFILL_ROWS = 8192      # rows (sequences x tokens) of one prompt slice
+    PREFILL_ROWS = 16384     # rows (sequences x tokens) of one prompt slice: the expert weights are expanded once per slice and layer
     MOE_BLOCK = 2048         # tokens per call of the expert kernel (256 when the weights are not FP4-packed)
     FUSED_ROUTER_ROWS = 512  # up to this many rows the norm, the router and the top-k run as one launch
 
@@ -317,6 +317,8 @@ class Transformer:
         if rows <= block:
             # a single call may leave the sum over a token's experts to the add + norm that follows it
             return ops.moe_experts_decode(n2, vals, idx, p.w1, p.w2, limit=self.config.swiglu_limit, defer_combine=True)
+        if ops._prefill_moe_ok(rows, p.w1, p.w2):   # prompt-sized: tokens as the M rows of a grouped GEMM
+            return ops.moe_experts_prefill(n2, vals, idx, p.w1, p.w2, limit=self.config.swiglu_limit)
         out = torch.empty_like(n2)
         for r0 in range(0, rows, block):
             r1 = min(rows, r0 + block)

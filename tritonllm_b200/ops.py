@@ -770,10 +770,56 @@ def _moe_from_reference(x, wg, w1, w1_mx, w2, w2_mx, bg, b1, b2, experts_per_tok
     return moe_experts(x, vals, idx, e1, e2, limit=swiglu_limit)
 
 
+_moe_prefill_ws: dict = {}
+PREFILL_MOE_MIN_TOKENS = 2049    # from here on the grouped GEMM (tokens as M rows) beats the decode-sized kernel
+
+
+def moe_experts_prefill(x, topk_vals, topk_idx, w1, w2, alpha=1.702, limit=7.0):
+    """moe_experts (tritonllm/gpt_oss/triton/moe.py:54-87) for a prompt-sized batch: x [T, hidden] bf16 with the
+    routing `topk` returned; w1 / w2 ExpertWeightsFp4.  The MXFP4 weights are expanded to bf16 into a scratch
+    (1.6 GB for the 20b shapes, kept per device and shape) and the tokens of every expert run through one grouped
+    tensor-core GEMM per projection.  Returns a new [T, hidden] bf16 tensor."""
+    _need_cuda(x, topk_vals, topk_idx)
+    assert isinstance(w1, ExpertWeightsFp4) and isinstance(w2, ExpertWeightsFp4)
+    assert x.dtype == _BF16 and x.dim() == 2 and x.stride(1) == 1
+    t, hidden = x.shape
+    assert topk_idx.dtype == torch.int16 and topk_vals.dtype == torch.float32
+    assert topk_idx.shape == (t, 4) and topk_vals.shape == (t, 4) and topk_idx.is_contiguous() and topk_vals.is_contiguous()
+    e, inter = w1.codes.shape[0], w1.n // 2
+    assert w1.k == hidden and (w2.n, w2.k) == (hidden, inter)
+    out = torch.empty((t, hidden), dtype=_BF16, device=x.device)
+    if t == 0:
+        return out
+    lib = _lib.load()
+    need = lib.b2_moe_prefill_workspace_bytes(t, e, hidden, inter)
+    key = (x.device, e, hidden, inter)
+    hit = _moe_prefill_ws.get(key)
+    if hit is None or hit[0].numel() < need:
+        hit = (torch.empty(need, dtype=torch.uint8, device=x.device),
+               torch.empty((e * 2 * inter, hidden), dtype=_BF16, device=x.device),
+               torch.empty((e * hidden, inter), dtype=_BF16, device=x.device))
+        _moe_prefill_ws[key] = hit
+    ws, w1b, w2b = hit
+    _lib.call("b2_moe_upcast_packed", w1.codes.data_ptr(), w1.sf.data_ptr(), w1b.data_ptr(), e, 2 * inter, hidden, _stream())
+    _lib.call("b2_moe_upcast_packed", w2.codes.data_ptr(), w2.sf.data_ptr(), w2b.data_ptr(), e, hidden, inter, _stream())
+    _lib.call("b2_moe_experts_prefill", x.data_ptr(), x.stride(0), topk_idx.data_ptr(), topk_vals.data_ptr(), w1b.data_ptr(),
+              w1.bias.data_ptr(), w2b.data_ptr(), w2.bias.data_ptr(), out.data_ptr(), out.stride(0), ws.data_ptr(), ws.numel(),
+              t, e, hidden, inter, float(alpha), float(limit), _stream())
+    return out
+
+
+def _prefill_moe_ok(t, w1, w2) -> bool:
+    return (isinstance(w1, ExpertWeightsFp4) and t >= PREFILL_MOE_MIN_TOKENS and w1.k % 192 == 0 and w1.n % 192 == 0
+            and w1.k % 8 == 0 and (w1.n // 2) % 8 == 0)
+
+
 def moe_experts(x, topk_vals, topk_idx, w1, w2, alpha=1.702, limit=7.0):
     """moe_experts (tritonllm/gpt_oss/triton/moe.py:54-87) for any number of tokens: the expert GEMMs of
-    x [T, hidden] with the routing `topk` returned, in calls of at most 2048 tokens."""
+    x [T, hidden] with the routing `topk` returned - the grouped tensor-core GEMM for prompt-sized batches, else the
+    decode-sized kernel in calls of at most 2048 tokens."""
     t = x.shape[0]
+    if _prefill_moe_ok(t, w1, w2):
+        return moe_experts_prefill(x, topk_vals, topk_idx, w1, w2, alpha=alpha, limit=limit)
     block = 2048 if isinstance(w1, ExpertWeightsFp4) else 256
     if t <= block:
         return moe_experts_decode(x, topk_vals, topk_idx, w1, w2, alpha=alpha, limit=limit)
