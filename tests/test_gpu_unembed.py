@@ -35,7 +35,7 @@ def test_unembed_golden():
     assert torch.equal(ids.cpu(), t(g["ids"]).long())       # includes the exact tie (rows 17 and 201): 17 wins
 
 
-@pytest.mark.parametrize("B,V,H", [(1, 201088, 2880), (32, 201088, 2880), (256, 50000, 2880), (5, 1000, 192), (300, 4096, 128)])
+@pytest.mark.parametrize("B,V,H", [(1, 201088, 2880), (32, 201088, 2880), (256, 50000, 2880), (5, 1000, 192), (300, 4096, 128), (200, 1100, 192)])
 def test_unembed_vs_oracle(B, V, H):
     ops = _ops()
     gen = torch.Generator().manual_seed(5000 + B)

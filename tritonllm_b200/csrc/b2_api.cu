@@ -30,6 +30,10 @@ static void init_tunables() {
     g_tunables[TUNE_MOE_FP4_TOK] = 0;      // 32 / 64: tokens of an expert per CTA (0: 32)
     g_tunables[TUNE_UNEMBED_STAGES] = 0;   // ring depth of the unembedding kernel (0: as deep as shared memory allows)
     g_tunables[TUNE_MOE_PREFETCH] = 0;     // k-blocks of expert weights requested into L2 ahead of the shared-memory ring (0: off; 3-12 measured no faster)
+    g_tunables[TUNE_ATTN_PREFILL_EXP16] = 0;   // 1: prefill attention computes its exponentials two at a time on fp16 pairs (measured slower)
+    g_tunables[TUNE_RMSNORM_WARPS] = 0;          // warps per CTA of the streaming RMSNorm (0: 16)
+    g_tunables[TUNE_RMSNORM_RING_MIN_ROWS] = 0;  // rows from which RMSNorm streams rows through shared memory (0: 512)
+    g_tunables[TUNE_UNEMBED_TILES] = 0;          // 1: one weight tile per CTA in the unembedding at every batch size (0: two above 128 sequences)
     g_tunables[TUNE_LAUNCH_OVERLAP] = 0;   // 1: decode kernels are launched with programmatic stream serialization
     g_tunables[TUNE_TMA_L2_PROMOTION] = 0;  // 0 none, 1 = 64 B, 2 = 128 B, 3 = 256 B
   }
@@ -191,7 +195,7 @@ B2_API int b2_set_tunable(const char* name, int value) {
   if (!name) return B2_ERR_NULL;
   b2::init_tunables();
   static const char* names[b2::TUNE_COUNT] = {"attn_decode_ctas_per_sm", "gemv_ksplit_qkv", "gemv_ksplit_out",
-                                                  "tma_l2_promotion", "attn_decode_stages", "gemm_pair", "moe_fp4_stages", "launch_overlap", "moe_fp4_tok", "unembed_stages", "moe_prefetch"};
+                                                  "tma_l2_promotion", "attn_decode_stages", "gemm_pair", "moe_fp4_stages", "launch_overlap", "moe_fp4_tok", "unembed_stages", "moe_prefetch", "attn_prefill_exp16", "rmsnorm_warps", "rmsnorm_ring_min_rows", "unembed_tiles"};
   for (int i = 0; i < b2::TUNE_COUNT; ++i) {
     if (std::strcmp(name, names[i]) == 0) {
       b2::g_tunables[i] = value;

@@ -47,6 +47,7 @@ enum { EPI_QKV = 0, EPI_OUT = 1, EPI_LOGITS = 2 };
 struct SkinnyArgs {
   const __nv_bfloat16* bias;
   int batch, bn, k_in, n_out, stages, n_tiles, nkb, epi, kslices;
+  int tpc;     // weight tiles per CTA (EPI_LOGITS with many sequences: 2, so that an activation tile fetched from L2 feeds two)
   int vec_ok;  // outputs, bias and residual allow 8-byte accesses at every multiple of four features
   // EPI_QKV
   const float* sin_tab;
@@ -112,15 +113,15 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   cg::cluster_group cluster = cg::this_cluster();
-  const int S = a.stages, bn = a.bn, KS = a.kslices;
-  const int stage_bytes = SK_W_BYTES + bn * SK_KB * 2;
+  const int S = a.stages, bn = a.bn, KS = a.kslices, TPC = a.tpc;
+  const int stage_bytes = TPC * SK_W_BYTES + bn * SK_KB * 2;
   // the ring memory is reused for the fp32 dump of the accumulator once the main loop is over
   const size_t ring_bytes = max(static_cast<size_t>(S) * stage_bytes, sk_dump_bytes(bn));
   SkinnySmem& sm = *reinterpret_cast<SkinnySmem*>(tiles + ((ring_bytes + 15) & ~static_cast<size_t>(15)));
   float* dump = reinterpret_cast<float*>(tiles);
   const int dstride = bn + 4;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int tile = blockIdx.x, rank = blockIdx.y;  // cluster = the K slices of one tile (along y)
+  const int tile = blockIdx.x * TPC, rank = blockIdx.y;  // first tile of the CTA; cluster = the K slices of one tile (along y)
 
   overlap_start();
   if (tid == 0 && a.trace) a.trace[(blockIdx.x * KS + rank) * 8 + 0] = global_timer_ns();
@@ -136,7 +137,7 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     tma_prefetch_desc(&tm_x);
   }
   int tmem_cols = 32;
-  while (tmem_cols < bn) tmem_cols <<= 1;
+  while (tmem_cols < TPC * bn) tmem_cols <<= 1;
   if (warp == 1) tmem_alloc(&sm.tmem_base, tmem_cols);
   tc_fence_before_sync();
   __syncthreads();
@@ -162,8 +163,9 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         }
         uint8_t* st = tiles + static_cast<size_t>(s) * stage_bytes;
         mbar_arrive_expect_tx(&sm.full[s], static_cast<uint32_t>(stage_bytes));
-        tma_load_2d(st, &tm_w, &sm.full[s], (kb_begin + i) * SK_KB, tile * SK_FT);
-        tma_load_2d(st + SK_W_BYTES, &tm_x, &sm.full[s], (kb_begin + i) * SK_KB, b0);
+        for (int h = 0; h < TPC; ++h)   // rows past n_out (an odd tile count) read as zero
+          tma_load_2d(st + h * SK_W_BYTES, &tm_w, &sm.full[s], (kb_begin + i) * SK_KB, (tile + h) * SK_FT);
+        tma_load_2d(st + TPC * SK_W_BYTES, &tm_x, &sm.full[s], (kb_begin + i) * SK_KB, b0);
         issued = i + 1;
       }
       if (*abort_flag) {
@@ -187,9 +189,12 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         }
         tc_fence_after_sync();
         const uint32_t sa = smem_u32(tiles + static_cast<size_t>(s) * stage_bytes);
-        const uint64_t dw = umma_desc_k128(sa), dx = umma_desc_k128(sa + SK_W_BYTES);
+        const uint64_t dx = umma_desc_k128(sa + TPC * SK_W_BYTES);
+        for (int h = 0; h < TPC; ++h) {
+          const uint64_t dw = umma_desc_k128(sa + h * SK_W_BYTES);
 #pragma unroll
-        for (int k = 0; k < SK_KB / 16; ++k) umma_bf16(tmem, dw + 2 * k, dx + 2 * k, idesc, (i | k) != 0);
+          for (int k = 0; k < SK_KB / 16; ++k) umma_bf16(tmem + h * bn, dw + 2 * k, dx + 2 * k, idesc, (i | k) != 0);
+        }
         umma_commit(&sm.empty[s]);
       }
       if (ok) {
@@ -199,24 +204,17 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         *abort_flag = 1;
       }
     }
-  } else {
-    // ================================ accumulator -> shared memory ================================
+  }
+  // ================================ accumulator -> shared memory (warps 2-5) ================================
+  bool acc_ok = true;
+  auto dump_acc = [&](int h) {   // accumulator of the CTA's h-th tile -> the ring memory, which is idle by now
     const int lane_grp = warp & 3;  // a warp may only read TMEM lanes 32*(warp%4) .. +31
     const int row = lane_grp * 32 + lane;
-    const uint32_t trow = tmem + (static_cast<uint32_t>(lane_grp * 32) << 16);
-    bool ok = n_my == 0 || mbar_wait_bounded(&sm.acc_full, 0, abort_flag);
-    ok = __all_sync(0xffffffffu, ok);
-    if (!ok) {
-      if (lane == 0 && !*abort_flag) atomicOr(a.status, B2_DEV_TIMEOUT_MMA);
-      *abort_flag = 1;
-    }
-    if (a.trace && tid == 64) a.trace[(blockIdx.x * KS + rank) * 8 + 2] = global_timer_ns();
-    tc_fence_after_sync();
-    // the ring is idle now (every stage was consumed before acc_full fired): overwrite it with the dump
+    const uint32_t trow = tmem + (static_cast<uint32_t>(lane_grp * 32) << 16) + h * bn;
     float* drow = dump + static_cast<size_t>(row) * dstride;
     for (int c = 0; c < bn; c += 32) {
       float v[32];
-      if (ok && n_my > 0) {
+      if (acc_ok && n_my > 0) {
         tmem_ld_32x32(trow + c, v);
       } else {
 #pragma unroll
@@ -230,32 +228,54 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         for (int i = 0; i < 32; ++i) dump[(c + i) * SK_TS + row] = v[i];
       }
     }
+  };
+  if (warp >= 2) {
+    acc_ok = n_my == 0 || mbar_wait_bounded(&sm.acc_full, 0, abort_flag);
+    acc_ok = __all_sync(0xffffffffu, acc_ok);
+    if (!acc_ok) {
+      if (lane == 0 && !*abort_flag) atomicOr(a.status, B2_DEV_TIMEOUT_MMA);
+      *abort_flag = 1;
+    }
+    if (a.trace && tid == 64) a.trace[(blockIdx.x * KS + rank) * 8 + 2] = global_timer_ns();
+    tc_fence_after_sync();
+    // the ring is idle now (every stage was consumed before acc_full fired): overwrite it with the dump
+    dump_acc(0);
   }
   tc_fence_before_sync();
   cluster.sync();  // every slice of the tile is in its CTA's shared memory
 
-  if (warp >= 2 && !*abort_flag && a.epi == EPI_LOGITS) {
+  if (warp >= 2 && a.epi == EPI_LOGITS) {
     // ================================ unembedding: logits and per-tile arg-max (one K slice per tile) ================================
     const int e = (warp - 2) * 32 + lane;  // 0..127
-    const int f = tile * SK_FT + e;
-    if (a.logits && f < a.n_out) {   // thread e owns vocabulary row e of the tile: for a sequence, 128 threads write 256 contiguous bytes
-      for (int c = 0; c < bn && b0 + c < a.batch; ++c)
-        a.logits[static_cast<size_t>(b0 + c) * a.logits_stride + f] = __float2bfloat16_rn(dump[e * dstride + c]);
-    }
-    if (a.part_max) {                // thread c owns sequence c: the largest fp32 sum of the tile, first row on ties
-      const int rows = min(SK_FT, a.n_out - tile * SK_FT);
-      for (int c = e; c < bn && b0 + c < a.batch; c += 128) {
-        float best = dump[c];
-        int arg = 0;
-        for (int r = 1; r < rows; ++r) {
-          const float v = dump[r * dstride + c];
-          if (v > best) {
-            best = v;
-            arg = r;
+    for (int h = 0; h < TPC; ++h) {
+      if (h > 0) {   // the next tile of this CTA: its accumulator replaces the dump once every thread is done with it
+        named_bar_sync(1, 128);
+        tc_fence_after_sync();
+        dump_acc(h);
+        named_bar_sync(1, 128);
+      }
+      const int t = tile + h;
+      const int f = t * SK_FT + e;
+      const int rows = min(SK_FT, a.n_out - t * SK_FT);
+      if (rows <= 0 || *abort_flag) continue;
+      if (a.logits && f < a.n_out) {   // thread e owns vocabulary row e of the tile: for a sequence, 128 threads write 256 contiguous bytes
+        for (int c = 0; c < bn && b0 + c < a.batch; ++c)
+          a.logits[static_cast<size_t>(b0 + c) * a.logits_stride + f] = __float2bfloat16_rn(dump[e * dstride + c]);
+      }
+      if (a.part_max) {                // thread c owns sequence c: the largest fp32 sum of the tile, first row on ties
+        for (int c = e; c < bn && b0 + c < a.batch; c += 128) {
+          float best = dump[c];
+          int arg = 0;
+          for (int r = 1; r < rows; ++r) {
+            const float v = dump[r * dstride + c];
+            if (v > best) {
+              best = v;
+              arg = r;
+            }
           }
+          a.part_max[static_cast<size_t>(t) * a.batch + b0 + c] = best;
+          a.part_idx[static_cast<size_t>(t) * a.batch + b0 + c] = t * SK_FT + arg;
         }
-        a.part_max[static_cast<size_t>(tile) * a.batch + b0 + c] = best;
-        a.part_idx[static_cast<size_t>(tile) * a.batch + b0 + c] = tile * SK_FT + arg;
       }
     }
   } else if (warp >= 2 && !*abort_flag) {
@@ -413,8 +433,8 @@ static int skinny_bn(int64_t batch) {
   return static_cast<int>((b + 31) / 32 * 32);
 }
 
-static size_t skinny_smem_bytes(int bn, int nkb, int ks, int* stages_out, int max_stages = SK_MAX_STAGES) {
-  const int stage_bytes = SK_W_BYTES + bn * SK_KB * 2;
+static size_t skinny_smem_bytes(int bn, int nkb, int ks, int* stages_out, int max_stages = SK_MAX_STAGES, int tpc = 1) {
+  const int stage_bytes = tpc * SK_W_BYTES + bn * SK_KB * 2;
   int stages = (200 * 1024) / stage_bytes;
   stages = stages > max_stages ? max_stages : stages;
   const int per_slice = (nkb + ks - 1) / ks;
@@ -508,18 +528,23 @@ static int launch_skinny(const void* x, int64_t x_stride, const void* w, SkinnyA
     // the unembedding has many more tiles than SMs: with half the ring two CTAs share an SM and one streams while
     // the other sets up or writes out (32 sequences: 267 -> 213 us); at 256 sequences a stage is too large for that
     int max_stages = SK_MAX_STAGES;
+    a.tpc = 1;
     if (a.epi == EPI_LOGITS) {
       const int forced = tunable(TUNE_UNEMBED_STAGES);
       const int stage_bytes = SK_W_BYTES + a.bn * SK_KB * 2;
       if (a.bn <= 128) max_stages = (108 * 1024) / stage_bytes;   // 5 / 4 / 3 stages at 32 / 64 / 128 sequences
       if (forced > 0) max_stages = forced > SK_MAX_STAGES ? SK_MAX_STAGES : forced;
+      // many sequences: the activation tile of a k-block (32 KB at 256 sequences) is twice the weight tile and every
+      // CTA re-reads it from L2, which then bounds the kernel; a CTA that takes two weight tiles halves that traffic
+      // (two accumulators of 256 columns fill tensor memory)
+      if (a.bn > 128 && tunable(TUNE_UNEMBED_TILES) != 1) a.tpc = 2;
     }
-    const size_t smem = skinny_smem_bytes(a.bn, a.nkb, ks, &a.stages, max_stages);
+    const size_t smem = skinny_smem_bytes(a.bn, a.nkb, ks, &a.stages, max_stages, a.tpc);
     cudaError_t e = cudaFuncSetAttribute(skinny_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(a.n_tiles, ks, 1);
+    cfg.gridDim = dim3((a.n_tiles + a.tpc - 1) / a.tpc, ks, 1);
     cfg.blockDim = dim3(SK_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;

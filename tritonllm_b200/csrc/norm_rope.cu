@@ -205,19 +205,15 @@ static int launch_rmsnorm_ring_w(const void* x, const void* delta, const float* 
   return launch_status();
 }
 
-// Warps per CTA: a warp takes whole rows, so with R rows over G CTAs of W warps the slowest warp does
-// ceil(R / (G W)) rows; of the widths that fit, take the one that wastes the least of that (8192 rows on 148 SMs:
-// 16 warps give 4 rows to a warp that has 3.46 on average, 8 warps give 7 for 6.92).
+// Warps per CTA: 16 (8 measured slower at 8192 rows although it balances the rows better: 32.8 against 26.4 us);
+// the tunable "rmsnorm_warps" (8 / 16 / 32) overrides it for experiments.
 template <bool ADD, int VPL>
 static int launch_rmsnorm_ring(const void* x, const void* delta, const float* gain, void* h_out, void* y_out,
                                int64_t rows, int dim, float eps, int* status, cudaStream_t stream) {
-  const auto waste = [&](int w) {
-    int64_t grid = (rows + w - 1) / w;
-    if (grid > sm_count()) grid = sm_count();
-    const int64_t slots = grid * w;
-    return static_cast<double>((rows + slots - 1) / slots * slots) / static_cast<double>(rows);
-  };
-  if (waste(8) + 0.03 < waste(16)) return launch_rmsnorm_ring_w<ADD, VPL, 8>(x, delta, gain, h_out, y_out, rows, dim, eps, status, stream);
+  const int w = tunable(TUNE_RMSNORM_WARPS);
+  if (w == 8) return launch_rmsnorm_ring_w<ADD, VPL, 8>(x, delta, gain, h_out, y_out, rows, dim, eps, status, stream);
+  if (w == 32 && static_cast<size_t>(dim) * 2 * (ADD ? 2 : 1) * 32 <= 200 * 1024)
+    return launch_rmsnorm_ring_w<ADD, VPL, 32>(x, delta, gain, h_out, y_out, rows, dim, eps, status, stream);
   return launch_rmsnorm_ring_w<ADD, VPL, 16>(x, delta, gain, h_out, y_out, rows, dim, eps, status, stream);
 }
 
@@ -232,7 +228,11 @@ static int launch_rmsnorm(const void* x, const void* delta, const float* gain, v
     return B2_ERR_ALIGN;
   const int nvec = dim / 8;
   const int vpl = (nvec + 31) / 32;
-  if (rows >= 512 && static_cast<size_t>(dim) * 2 * (ADD ? 2 : 1) * 16 <= 200 * 1024) {
+  // The ring of bulk copies pays off where a row needs two input streams (the fused add: 37.9 against 45.1 us at
+  // 8192 rows); a plain norm is faster with one warp per row on ordinary 128-bit loads at every size measured
+  // (8192 rows: 21.0 against 26.1 us; 65536 rows: 117.8 against 141.3 us = 0.99 of the copy bandwidth).
+  const int ring_min = tunable(TUNE_RMSNORM_RING_MIN_ROWS) > 0 ? tunable(TUNE_RMSNORM_RING_MIN_ROWS) : (ADD ? 512 : 0x7fffffff);
+  if (rows >= ring_min && static_cast<size_t>(dim) * 2 * (ADD ? 2 : 1) * 16 <= 200 * 1024) {
     // streaming case: per-warp rings of row buffers in shared memory
     int* status = device_status_ptr();
     if (!status) return B2_ERR_DRIVER;

@@ -230,6 +230,30 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+// Two exponentials per special-function instruction: the arguments as an fp16 pair (11 significant bits: an
+// argument below 16 in magnitude is off by at most 2^-8, i.e. 0.3 % of a result that is itself below 2^-8 of the
+// row maximum whenever the argument is that large), the results as an fp16 pair.
+__device__ __forceinline__ uint32_t f32x2_to_f16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ uint32_t ex2_f16x2(uint32_t x) {
+  uint32_t y;
+  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+__device__ __forceinline__ float f16lo_to_f32(uint32_t v) {
+  float f;
+  asm("{ .reg .b16 l, h; mov.b32 {l, h}, %1; cvt.f32.f16 %0, l; }" : "=f"(f) : "r"(v));
+  return f;
+}
+__device__ __forceinline__ float f16hi_to_f32(uint32_t v) {
+  float f;
+  asm("{ .reg .b16 l, h; mov.b32 {l, h}, %1; cvt.f32.f16 %0, h; }" : "=f"(f) : "r"(v));
+  return f;
+}
+
 // 32 lanes x 16 columns store: thread i writes lane (base + i), columns c..c+15.
 __device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile(
