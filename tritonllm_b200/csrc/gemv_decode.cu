@@ -106,6 +106,9 @@ __device__ __forceinline__ void st_bf16x4(__nv_bfloat16* p, bool vec, int n, con
   }
 }
 
+// TPC = weight tiles per CTA: 1, or 2 for the unembedding with many sequences (a compile-time constant so that the
+// common instantiation keeps straight-line producer / MMA code).
+template <int TPC>
 __global__ void __launch_bounds__(SK_THREADS, 1)
 skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const SkinnyArgs a,
                  int b0) {
@@ -113,7 +116,7 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   cg::cluster_group cluster = cg::this_cluster();
-  const int S = a.stages, bn = a.bn, KS = a.kslices, TPC = a.tpc;
+  const int S = a.stages, bn = a.bn, KS = a.kslices;
   const int stage_bytes = TPC * SK_W_BYTES + bn * SK_KB * 2;
   // the ring memory is reused for the fp32 dump of the accumulator once the main loop is over
   const size_t ring_bytes = max(static_cast<size_t>(S) * stage_bytes, sk_dump_bytes(bn));
@@ -163,6 +166,7 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         }
         uint8_t* st = tiles + static_cast<size_t>(s) * stage_bytes;
         mbar_arrive_expect_tx(&sm.full[s], static_cast<uint32_t>(stage_bytes));
+#pragma unroll
         for (int h = 0; h < TPC; ++h)   // rows past n_out (an odd tile count) read as zero
           tma_load_2d(st + h * SK_W_BYTES, &tm_w, &sm.full[s], (kb_begin + i) * SK_KB, (tile + h) * SK_FT);
         tma_load_2d(st + TPC * SK_W_BYTES, &tm_x, &sm.full[s], (kb_begin + i) * SK_KB, b0);
@@ -190,6 +194,7 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         tc_fence_after_sync();
         const uint32_t sa = smem_u32(tiles + static_cast<size_t>(s) * stage_bytes);
         const uint64_t dx = umma_desc_k128(sa + TPC * SK_W_BYTES);
+#pragma unroll
         for (int h = 0; h < TPC; ++h) {
           const uint64_t dw = umma_desc_k128(sa + h * SK_W_BYTES);
 #pragma unroll
@@ -295,42 +300,23 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     // contiguous bytes of each slice's dump and write runs of 64-128 contiguous bytes of the output row;
     // this CTA takes every KS-th group of 128 items
     const int items = bn * 16;
-    // An item's operands (bias, rotation, residual, destination) and then its slices' sums.  Two items are in flight
-    // per thread: the global loads of both are issued before either's remote shared-memory reads, so a thread waits
-    // once per pair instead of once per item (at 256 sequences a thread has about ten items).
-    struct Item {
-      bool live;
-      int c, r_lo, r_hi, n_lo, n_hi;
-      bool rotate;
-      float bias_lo[4], bias_hi[4], cs[4], sn[4], res_lo[4], res_hi[4];
-      __nv_bfloat16* dst_lo;
-      __nv_bfloat16* dst_hi;
-      float4 lo, hi;
-    };
-    auto prep = [&](int it, Item& I) {
-      I.live = false;
-      I.dst_lo = I.dst_hi = nullptr;
-      if (it >= items) return;
+    for (int it = rank * 128 + e; it < items; it += KS * 128) {
       const int c = it >> 4, qd = it & 15;
       const int b = b0 + c;
-      if (b >= a.batch) return;
-      I.c = c;
-      I.r_lo = a.epi == EPI_QKV ? ((qd >> 3) * 64 + (qd & 7) * 4) : qd * 4;  // RoPE pair (j, j+32) / rows (r, r+64)
-      I.r_hi = a.epi == EPI_QKV ? I.r_lo + 32 : I.r_lo + 64;
-      const int f_lo = tile * SK_FT + I.r_lo, f_hi = tile * SK_FT + I.r_hi;
-      I.n_lo = min(4, a.n_out - f_lo);
-      I.n_hi = min(4, a.n_out - f_hi);   // valid features of each quad
-      if (I.n_lo <= 0) return;
-      I.live = true;
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        I.cs[q] = 1.f;
-        I.sn[q] = 0.f;
-        I.res_lo[q] = I.res_hi[q] = 0.f;
-      }
-      ld_bf16x4(a.bias + f_lo, a.vec_ok, I.n_lo, I.bias_lo);
-      ld_bf16x4(a.bias + f_hi, a.vec_ok, I.n_hi, I.bias_hi);
-      I.rotate = false;
+      if (b >= a.batch) continue;
+      const int r_lo = a.epi == EPI_QKV ? ((qd >> 3) * 64 + (qd & 7) * 4) : qd * 4;  // RoPE pair (j, j+32) / rows (r, r+64)
+      const int r_hi = a.epi == EPI_QKV ? r_lo + 32 : r_lo + 64;
+      const int f_lo = tile * SK_FT + r_lo, f_hi = tile * SK_FT + r_hi;
+      const int n_lo = min(4, a.n_out - f_lo), n_hi = min(4, a.n_out - f_hi);   // valid features of each quad
+      if (n_lo <= 0) continue;
+      // epilogue operands first, so their latency overlaps the remote shared-memory reads
+      float bias_lo[4], bias_hi[4], cs[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
+      float res_lo[4] = {0.f, 0.f, 0.f, 0.f}, res_hi[4] = {0.f, 0.f, 0.f, 0.f};
+      ld_bf16x4(a.bias + f_lo, a.vec_ok, n_lo, bias_lo);
+      ld_bf16x4(a.bias + f_hi, a.vec_ok, n_hi, bias_hi);
+      __nv_bfloat16* dst_lo = nullptr;
+      __nv_bfloat16* dst_hi = nullptr;
+      bool rotate = false;
       long long kv_row = static_cast<long long>(b) * a.cs_b + offset * a.cs_n;   // element offset of the token's K/V row
       if (per_seq) {   // this sequence's own position, and its page when the KV store is paged
         offset = a.offset[static_cast<size_t>(b) * a.offset_stride];
@@ -352,72 +338,57 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       }
       if (a.epi == EPI_QKV) {
         const int head = tile * 2 + (qd >> 3), jj = (qd & 7) * 4;
-        I.rotate = head < a.n_q + a.n_kv;
-        if (I.rotate && a.vec_ok) {
+        rotate = head < a.n_q + a.n_kv;
+        if (rotate && a.vec_ok) {
           const float4 c4 = __ldg(reinterpret_cast<const float4*>(a.cos_tab + pos * 32 + jj));
           const float4 s4 = __ldg(reinterpret_cast<const float4*>(a.sin_tab + pos * 32 + jj));
-          I.cs[0] = c4.x; I.cs[1] = c4.y; I.cs[2] = c4.z; I.cs[3] = c4.w;
-          I.sn[0] = s4.x; I.sn[1] = s4.y; I.sn[2] = s4.z; I.sn[3] = s4.w;
-        } else if (I.rotate) {
+          cs[0] = c4.x; cs[1] = c4.y; cs[2] = c4.z; cs[3] = c4.w;
+          sn[0] = s4.x; sn[1] = s4.y; sn[2] = s4.z; sn[3] = s4.w;
+        } else if (rotate) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            I.cs[q] = __ldg(a.cos_tab + pos * 32 + jj + q);
-            I.sn[q] = __ldg(a.sin_tab + pos * 32 + jj + q);
+            cs[q] = __ldg(a.cos_tab + pos * 32 + jj + q);
+            sn[q] = __ldg(a.sin_tab + pos * 32 + jj + q);
           }
         }
         if (head < a.n_q) {
-          I.dst_lo = a.q_out + (static_cast<size_t>(b) * a.n_q + head) * 64 + jj;
+          dst_lo = a.q_out + (static_cast<size_t>(b) * a.n_q + head) * 64 + jj;
         } else if (offset_ok) {
           const bool is_k = head < a.n_q + a.n_kv;
           const int kvh = is_k ? head - a.n_q : head - a.n_q - a.n_kv;
-          I.dst_lo = (is_k ? a.cache_k : a.cache_v) + kv_row + kvh * a.cs_h + jj;
+          dst_lo = (is_k ? a.cache_k : a.cache_v) + kv_row + kvh * a.cs_h + jj;
         }
-        I.dst_hi = I.dst_lo ? I.dst_lo + 32 : nullptr;
+        dst_hi = dst_lo ? dst_lo + 32 : nullptr;
       } else {
         __nv_bfloat16* res = a.residual + static_cast<size_t>(b) * a.res_stride;
-        I.dst_lo = res + f_lo;
-        I.dst_hi = res + f_hi;
-        ld_bf16x4(I.dst_lo, a.vec_ok, I.n_lo, I.res_lo);
-        ld_bf16x4(I.dst_hi, a.vec_ok, I.n_hi, I.res_hi);
+        dst_lo = res + f_lo;
+        dst_hi = res + f_hi;
+        ld_bf16x4(dst_lo, a.vec_ok, n_lo, res_lo);
+        ld_bf16x4(dst_hi, a.vec_ok, n_hi, res_hi);
       }
-    };
-    auto gather = [&](Item& I) {   // the slices' partial sums, fixed order: deterministic
-      I.lo = make_float4(0.f, 0.f, 0.f, 0.f);
-      I.hi = I.lo;
-      if (!I.live) return;
-      for (int rr = 0; rr < KS; ++rr) {
-        const float* remote = cluster.map_shared_rank(dump, rr) + I.c * SK_TS;
-        const float4 pl = *reinterpret_cast<const float4*>(remote + I.r_lo);
-        const float4 ph = *reinterpret_cast<const float4*>(remote + I.r_hi);
-        I.lo.x += pl.x; I.lo.y += pl.y; I.lo.z += pl.z; I.lo.w += pl.w;
-        I.hi.x += ph.x; I.hi.y += ph.y; I.hi.z += ph.z; I.hi.w += ph.w;
+      float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
+      for (int rr = 0; rr < KS; ++rr) {  // fixed order: deterministic sums
+        const float* remote = cluster.map_shared_rank(dump, rr) + c * SK_TS;
+        const float4 pl = *reinterpret_cast<const float4*>(remote + r_lo);
+        const float4 ph = *reinterpret_cast<const float4*>(remote + r_hi);
+        lo.x += pl.x; lo.y += pl.y; lo.z += pl.z; lo.w += pl.w;
+        hi.x += ph.x; hi.y += ph.y; hi.z += ph.z; hi.w += ph.w;
       }
-    };
-    auto finish = [&](Item& I) {
-      if (!I.live || !I.dst_lo) return;  // (K/V of a position outside the cache: nothing is written)
-      float vl[4] = {I.lo.x + I.bias_lo[0], I.lo.y + I.bias_lo[1], I.lo.z + I.bias_lo[2], I.lo.w + I.bias_lo[3]};
-      float vh[4] = {I.hi.x + I.bias_hi[0], I.hi.y + I.bias_hi[1], I.hi.z + I.bias_hi[2], I.hi.w + I.bias_hi[3]};
+      if (!dst_lo) continue;  // K/V of a position outside the cache: nothing is written
+      float vl[4] = {lo.x + bias_lo[0], lo.y + bias_lo[1], lo.z + bias_lo[2], lo.w + bias_lo[3]};
+      float vh[4] = {hi.x + bias_hi[0], hi.y + bias_hi[1], hi.z + bias_hi[2], hi.w + bias_hi[3]};
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        if (I.rotate) {
-          const float rl = vl[q] * I.cs[q] - vh[q] * I.sn[q], rh = vh[q] * I.cs[q] + vl[q] * I.sn[q];
+        if (rotate) {
+          const float rl = vl[q] * cs[q] - vh[q] * sn[q], rh = vh[q] * cs[q] + vl[q] * sn[q];
           vl[q] = rl;
           vh[q] = rh;
         }
-        vl[q] += I.res_lo[q];
-        vh[q] += I.res_hi[q];
+        vl[q] += res_lo[q];
+        vh[q] += res_hi[q];
       }
-      st_bf16x4(I.dst_lo, a.vec_ok, I.n_lo, vl);
-      st_bf16x4(I.dst_hi, a.vec_ok, I.n_hi, vh);
-    };
-    for (int it = rank * 128 + e; it < items; it += 2 * KS * 128) {
-      Item A, B;
-      prep(it, A);
-      prep(it + KS * 128, B);
-      gather(A);
-      gather(B);
-      finish(A);
-      finish(B);
+      st_bf16x4(dst_lo, a.vec_ok, n_lo, vl);
+      st_bf16x4(dst_hi, a.vec_ok, n_hi, vh);
     }
   }
   cluster.sync();  // peers may still be reading this CTA's shared memory
@@ -461,7 +432,7 @@ static int choose_kslices(int n_tiles, int nkb, int bn) {
   if (start > nkb) start = nkb;
   for (int ks = start; ks >= 1; --ks) {
     const size_t smem = skinny_smem_bytes(bn, nkb, ks, nullptr);
-    if (cudaFuncSetAttribute(skinny_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
+    if (cudaFuncSetAttribute(skinny_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
         cudaSuccess) {
       (void)cudaGetLastError();
       continue;
@@ -478,7 +449,7 @@ static int choose_kslices(int n_tiles, int nkb, int bn) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int n_clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&n_clusters, skinny_tc_kernel, &cfg) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveClusters(&n_clusters, skinny_tc_kernel<1>, &cfg) != cudaSuccess) {
       (void)cudaGetLastError();
       continue;
     }
@@ -540,8 +511,10 @@ static int launch_skinny(const void* x, int64_t x_stride, const void* w, SkinnyA
       if (a.bn > 128 && tunable(TUNE_UNEMBED_TILES) != 1) a.tpc = 2;
     }
     const size_t smem = skinny_smem_bytes(a.bn, a.nkb, ks, &a.stages, max_stages, a.tpc);
-    cudaError_t e = cudaFuncSetAttribute(skinny_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(smem));
+    cudaError_t e = a.tpc == 2 ? cudaFuncSetAttribute(skinny_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                      static_cast<int>(smem))
+                               : cudaFuncSetAttribute(skinny_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                      static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((a.n_tiles + a.tpc - 1) / a.tpc, ks, 1);
@@ -557,7 +530,8 @@ static int launch_skinny(const void* x, int64_t x_stride, const void* w, SkinnyA
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = tunable(TUNE_LAUNCH_OVERLAP) ? 2 : 1;
-    e = cudaLaunchKernelEx(&cfg, skinny_tc_kernel, tm_w, tm_x, a, b0);
+    e = a.tpc == 2 ? cudaLaunchKernelEx(&cfg, skinny_tc_kernel<2>, tm_w, tm_x, a, b0)
+                   : cudaLaunchKernelEx(&cfg, skinny_tc_kernel<1>, tm_w, tm_x, a, b0);
     if (e != cudaSuccess) {
       (void)cudaGetLastError();
       return static_cast<int>(e);

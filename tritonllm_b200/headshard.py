@@ -54,6 +54,8 @@ def gather_heads(o_local: torch.Tensor, group=None) -> torch.Tensor:
     """All-gather of the per-rank attention outputs [rows, f_local] into [rows, world * f_local], rank r's features
     at columns r*f_local .. (heads are owned in rank order, so this is the layout o_proj expects).  One collective;
     the gathered data lands in this rank's own memory before anything reads it."""
+    if not dist.is_initialized():      # a single process: nothing to gather
+        return o_local
     world = dist.get_world_size(group)
     if world == 1:
         return o_local
