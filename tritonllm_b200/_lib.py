@@ -96,6 +96,12 @@ def load() -> C.CDLL:
         for name, (res, args) in PROTOTYPES.items():
             fn = getattr(lib, name)  # AttributeError here = header and library disagree
             fn.restype, fn.argtypes = res, args
+        # TRITONLLM_B200_TUNE="name=value,name=value": tuning knobs applied once at load (unknown names are an error)
+        for kv in filter(None, os.environ.get("TRITONLLM_B200_TUNE", "").split(",")):
+            name, _, value = kv.partition("=")
+            st = lib.b2_set_tunable(name.strip().encode(), int(value))
+            if st != 0:
+                raise RuntimeError(f"TRITONLLM_B200_TUNE: cannot set {kv!r} (status {st})")
         _lib = lib
     return _lib
 

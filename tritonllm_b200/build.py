@@ -25,7 +25,7 @@ LIB_PATH = os.path.join(LIB_DIR, "libtritonllm_b200.so")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr", "-Xptxas", "-v",
-]
+] + os.environ.get("TRITONLLM_B200_NVCC_FLAGS", "").split()   # e.g. -DAP_PHASE_TRACE=1 for a diagnostic build
 
 
 def _nvcc() -> str:

@@ -5,27 +5,32 @@
 // At head_dim 64 the exponential unit, not the tensor pipe, is the first limit (one exp per score
 // against 256 flops), so the kernel is organised around keeping the softmax warps busy.  A work unit is
 // 128 consecutive query tokens of one query head; the kernel is persistent: two CTAs per SM (half of
-// tensor memory and ~97 KiB of shared memory each) walk the unit list, heaviest units (latest
+// tensor memory and ~112 KiB of shared memory each) walk the unit list, heaviest units (latest
 // positions) first and in serpentine order so that every CTA gets the same mix.  Inside a CTA
 //   warp 0   : TMA producer, whole-warp loop with one elected lane issuing: the Q tile of each unit
 //              (two buffers, so the next unit's Q arrives early), then K and V blocks (64 keys x 64 dims,
-//              128-byte rows, 128B swizzle) through a four-stage ring that runs across unit
+//              128-byte rows, 128B swizzle) through a five-stage ring that runs across unit
 //              boundaries, straight from the [B, T, H, 64] layout;
 //   warp 1   : walks the block list as a whole warp (descriptors stay warp-uniform), one elected lane
-//              issues the tcgen05 MMAs: S_j = Q K_j^T (M=128, N=64, K=64) into one of two S buffers in
-//              tensor memory, always two blocks ahead of the softmax - also across a unit boundary -
+//              issues the tcgen05 MMAs: S_j = Q K_j^T (M=128, N=64, K=64) into one of three S buffers in
+//              tensor memory, always three blocks ahead of the softmax - also across a unit boundary -
 //              and O += P_j V_j (M=128, N=64, K=64) with P_j read from tensor memory (the A operand),
 //              V_j as an MN-major shared-memory operand and O accumulating in tensor memory;
 //   warps 2-5: one thread per query row: S row -> registers in one pass, row max, exp2 on the
-//              special-function unit, row sum, bf16 pack into one of two P buffers.  The running
-//              maximum is only advanced (and O rescaled in tensor memory) when it grows by more than
-//              2^8, so the rescale is rare.  Blocks that touch the causal diagonal, the window edge or
-//              the end of the keys carry a second bf16 term of P (parked in the S buffer the scores
-//              came from), so rows with few visible keys keep fp32-like weights.  After the last block
-//              of a unit they read O, hand the accumulator back to the MMA warp and store the rows.
-// The tensor pipe executes one thread's MMAs in issue order, which is what lets S_{j+2} overwrite the
-// buffer of S_j right after P_j V_j has been issued.  The sink logit joins the denominator at the
-// end.  All waits are bounded.
+//              special-function unit, row sum, bf16 pack of P_j over the first half of the buffer S_j
+//              came from.  The running maximum is only advanced (and O rescaled in tensor memory) when
+//              it grows by more than 2^8, so the rescale is rare.  Blocks that touch the causal
+//              diagonal, the window edge or the end of the keys carry a second bf16 term of P (in the
+//              second half of the same buffer), so rows with few visible keys keep fp32-like weights.
+//              After the last block of a unit they read O, hand the accumulator back to the MMA warp
+//              and store the rows.
+// The tensor pipe executes one thread's MMAs in issue order, which is what lets S_{j+3} overwrite the
+// buffer of S_j / P_j right after P_j V_j has been issued, with no barrier in between.  The round trip
+// "P written -> MMA warp wakes -> P V and Q K issued behind the other CTA's MMAs -> completion seen by
+// the softmax warps" was measured at about 1300 clocks against 1800 per block: with two S buffers and
+// separate P buffers every block waited some 250 clocks for its S and again for its P buffer; the
+// third buffer takes both waits off the softmax warps' path.  The sink logit joins the denominator at
+// the end.  All waits are bounded.
 #include <math_constants.h>
 
 #include <algorithm>
@@ -38,14 +43,16 @@ constexpr int AP_BM = 128;       // query rows per unit
 constexpr int AP_BN = 64;        // keys per block
 constexpr int AP_D = 64;
 constexpr int AP_THREADS = 192;
-constexpr int AP_STAGES = 4;     // K+V blocks in flight per CTA
+constexpr int AP_STAGES = 5;     // K+V blocks in flight per CTA (S = Q K^T runs three blocks ahead of O += P V)
+constexpr int AP_NSP = 3;        // S / P buffers in tensor memory
 constexpr int AP_Q_BYTES = AP_BM * AP_D * 2;     // 16 KiB
 constexpr int AP_KV_BYTES = AP_BN * AP_D * 2;    // 8 KiB
 constexpr float AP_M_INIT = -1.0e30f;
 constexpr float AP_RESCALE_STEP = 8.0f;          // log2 units the maximum may lag behind
-// tensor-memory columns of a CTA: two S buffers (64 fp32 each), two P buffers (32 each: 64 bf16 packed
-// in pairs), O (64 fp32)
-constexpr uint32_t AP_COL_S = 0, AP_COL_P = 128, AP_COL_O = 192, AP_TMEM_COLS = 256;
+// tensor-memory columns of a CTA: three S buffers (64 fp32 each; P_j, 64 bf16 packed in pairs, overwrites columns
+// 0..31 of the buffer of S_j and its second term columns 32..63), O (64 fp32)
+constexpr uint32_t AP_COL_S = 0, AP_COL_O = AP_NSP * AP_BN, AP_TMEM_COLS = 256;
+static_assert(AP_COL_O + AP_D <= AP_TMEM_COLS, "tensor-memory budget of one of two CTAs per SM");
 
 struct AttnPrefillArgs {
   const void* sinks;
@@ -59,7 +66,21 @@ struct AttnPrefillArgs {
   long long* trace;     // optional [CTA][8] (b2_set_trace_buffer): start ns, end ns, units, blocks
 };
 
-struct __align__(1024) AttnPrefillSmem {
+// Diagnostic build (-DAP_PHASE_TRACE=1): softmax warp 2 of every CTA adds up the SM clocks it spends per phase of a
+// block into trace slots 4..7 (wait for S, tensor-memory load, maximum + wait for the P buffer, exponentials + stores)
+// and slot 2 (its whole loop in the low 32 bits, store drain + arrive in the high 32 bits).
+#ifndef AP_PHASE_TRACE
+#define AP_PHASE_TRACE 0
+#endif
+#if AP_PHASE_TRACE
+#define AP_CLK(var) const uint32_t var = static_cast<uint32_t>(clock())
+#define AP_ACC(acc, t1, t0) acc += (t1) - (t0)
+#else
+#define AP_CLK(var)
+#define AP_ACC(acc, t1, t0)
+#endif
+
+struct AttnPrefillSmem {   // placed at the 1024-byte aligned start of dynamic shared memory
   uint8_t q[2][AP_Q_BYTES];
   uint8_t k[AP_STAGES][AP_KV_BYTES];
   uint8_t v[AP_STAGES][AP_KV_BYTES];
@@ -67,9 +88,9 @@ struct __align__(1024) AttnPrefillSmem {
   uint64_t q_empty[2];  // MMA -> producer: every S = Q K^T of the unit has been computed
   uint64_t kv_full[AP_STAGES];
   uint64_t kv_empty[AP_STAGES];
-  uint64_t s_full[2];   // MMA -> softmax: S_j is in S buffer j&1
-  uint64_t p_full[2];   // softmax -> MMA: P_j is in P buffer j&1 (and S_j has been copied out)
-  uint64_t pv_done[2];  // MMA -> softmax: O += P_j V_j has completed (P buffer j&1 may be rewritten)
+  uint64_t s_full[AP_NSP];   // MMA -> softmax: S_j is in buffer j%3
+  uint64_t p_full[AP_NSP];   // softmax -> MMA: P_j is in buffer j%3
+  uint64_t pv_done[2];  // MMA -> softmax: O += P_j V_j has completed (slot j&1; needed to rescale or read O)
   uint64_t o_free;      // softmax -> MMA: O of the finished unit has been read
   uint32_t tmem_base;
   int abort_flag;
@@ -127,10 +148,13 @@ template <bool EXP16>
 __global__ void __launch_bounds__(AP_THREADS, 2)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const AttnPrefillArgs a) {
-  extern __shared__ uint8_t smem_raw[];
-  AttnPrefillSmem& sm = *reinterpret_cast<AttnPrefillSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                                            ~static_cast<uintptr_t>(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  AttnPrefillSmem& sm = *reinterpret_cast<AttnPrefillSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if ((smem_u32(smem_raw) & 1023u) != 0) {  // the swizzled tiles need this alignment; never seen to fail
+    if (tid == 0) atomicOr(a.status, B2_DEV_BAD_INDEX);
+    return;
+  }
 
   // A launch that follows a failed wait on this device does nothing: the status word stays set until the
   // host has read and cleared it, so a failure costs one time limit, not one per CTA.
@@ -146,9 +170,11 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     for (int s = 0; s < 2; ++s) {
       mbar_init(&sm.q_full[s], 1);
       mbar_init(&sm.q_empty[s], 1);
+      mbar_init(&sm.pv_done[s], 1);
+    }
+    for (int s = 0; s < AP_NSP; ++s) {
       mbar_init(&sm.s_full[s], 1);
       mbar_init(&sm.p_full[s], 4);
-      mbar_init(&sm.pv_done[s], 1);
     }
     mbar_init(&sm.o_free, 4);
     sm.abort_flag = 0;
@@ -223,7 +249,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     }
   } else if (warp == 1) {
     // ===================================== MMA issuer =====================================
-    // Two cursors over the CTA's flat stream of blocks: S = Q K^T runs two blocks ahead of O += P V,
+    // Two cursors over the CTA's flat stream of blocks: S = Q K^T runs three blocks ahead of O += P V,
     // across unit boundaries too.
     const bool leader = elect_one();
     constexpr uint32_t IDESC_QK = umma_idesc_bf16(AP_BM, AP_BN);
@@ -271,25 +297,25 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       tc_fence_after_sync();
       const uint64_t dq = umma_desc_k128(smem_u32(sm.q[qb]));
       const uint64_t dk = umma_desc_k128(smem_u32(sm.k[c.g % AP_STAGES]));
-      const uint32_t ts = tmem + AP_COL_S + (c.g & 1) * AP_BN;
+      const uint32_t ts = tmem + AP_COL_S + (c.g % AP_NSP) * AP_BN;
       if (leader) {
 #pragma unroll
         for (int k = 0; k < AP_D / 16; ++k) umma_bf16(ts, dq + 2 * k, dk + 2 * k, IDESC_QK, k != 0);
-        umma_commit(&sm.s_full[c.g & 1]);
+        umma_commit(&sm.s_full[c.g % AP_NSP]);
         if (c.j == c.w.nblk - 1) umma_commit(&sm.q_empty[qb]);  // the unit's Q tile is no longer needed
       }
       __syncwarp();
       return true;
     };
-    for (int ahead = 0; ahead < 2 && ok && cq.valid; ++ahead) {
+    for (int ahead = 0; ahead < AP_NSP && ok && cq.valid; ++ahead) {
       ok = wait_kv(cq) && issue_qk(cq);
       if (ok) advance(cq);
     }
     while (ok && cp.valid) {
-      // K of the block two ahead is usually there long before P of this one: take that wait off the critical path
+      // K of the block three ahead is usually there long before P of this one: take that wait off the critical path
       if (cq.valid) ok = wait_kv(cq);
       if (!ok) break;
-      ok = __all_sync(0xffffffffu, mbar_wait_bounded(&sm.p_full[cp.g & 1], (cp.g >> 1) & 1, abort_flag));
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(&sm.p_full[cp.g % AP_NSP], (cp.g / AP_NSP) & 1, abort_flag));
       if (!ok) break;
       if (cp.j == 0 && cp.ui > 0) {  // the previous unit's O must have been read out
         ok = __all_sync(0xffffffffu, mbar_wait_bounded(&sm.o_free, (cp.ui - 1) & 1, abort_flag));
@@ -298,14 +324,14 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       tc_fence_after_sync();
       const int s = cp.g % AP_STAGES;
       const uint64_t dv = umma_desc_k128(smem_u32(sm.v[s]));
-      const uint32_t tp = tmem + AP_COL_P + (cp.g & 1) * (AP_BN / 2);
-      const uint32_t tl = tmem + AP_COL_S + (cp.g & 1) * AP_BN;
+      const uint32_t tp = tmem + AP_COL_S + (cp.g % AP_NSP) * AP_BN;   // P_j: first half of the buffer S_j came in
+      const uint32_t tl = tp + AP_BN / 2;                              // its second bf16 term: second half
       const bool masked = ap_block_is_masked(a, cp.w, cp.j);
       if (leader) {
 #pragma unroll
         for (int k = 0; k < AP_BN / 16; ++k)  // 16 keys: 8 packed P columns, 16 V rows (2048 B)
           umma_bf16_ts(tmem + AP_COL_O, tp + 8 * k, dv + 128 * k, IDESC_PV, (cp.j | k) != 0);
-        if (masked) {  // second bf16 term of P, parked in the S buffer of this block
+        if (masked) {  // second bf16 term of P
 #pragma unroll
           for (int k = 0; k < AP_BN / 16; ++k) umma_bf16_ts(tmem + AP_COL_O, tl + 8 * k, dv + 128 * k, IDESC_PV, 1u);
         }
@@ -313,7 +339,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         umma_commit(&sm.pv_done[cp.g & 1]);
       }
       __syncwarp();
-      // the S buffer of this block is free for the block two ahead: the pipe runs it after the MMAs just issued
+      // the buffer of this block is free for the block three ahead: the pipe runs it after the MMAs just issued
       if (cq.valid) {
         ok = issue_qk(cq);
         if (ok) advance(cq);
@@ -338,6 +364,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       dead = true;
     };
 
+#if AP_PHASE_TRACE
+    uint32_t ph_s = 0, ph_ld = 0, ph_mx = 0, ph_ex = 0, ph_st = 0, ph_pw = 0;
+    const uint32_t ph_begin = static_cast<uint32_t>(clock());
+#endif
     for (int i = 0; !dead; ++i) {
       const int u = ap_unit_index(i);
       if (u >= a.n_units) break;
@@ -356,18 +386,23 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       float m_run = AP_M_INIT, l_run = 0.f;
       for (int j = 0; j < w.nblk && !dead; ++j) {
         const int g = g0 + j;
-        const int buf = g & 1;
-        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&sm.s_full[buf], (g >> 1) & 1, abort_flag))) {
+        const int buf = g % AP_NSP;
+        AP_CLK(c0);
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&sm.s_full[buf], (g / AP_NSP) & 1, abort_flag))) {
           give_up();
           break;
         }
         tc_fence_after_sync();
+        AP_CLK(c1);
+        AP_ACC(ph_s, c1, c0);
         // ---- the whole S row of this thread, one pass
         float sv[AP_BN];
         const uint32_t ts = trow + AP_COL_S + buf * AP_BN;
         tmem_ld_32x32_nowait(ts, *reinterpret_cast<float(*)[32]>(&sv[0]));
         tmem_ld_32x32_nowait(ts + 32, *reinterpret_cast<float(*)[32]>(&sv[32]));
         tmem_wait_ld();
+        AP_CLK(c2);
+        AP_ACC(ph_ld, c2, c1);
         const bool masked = ap_block_is_masked(a, w, j);
         if (masked) {
           const int key0 = (w.blk_lo + j) * AP_BN;
@@ -397,16 +432,12 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           alpha = ex2_approx(m_run - m_blk);
           m_run = m_blk;
         }
-        // P buffer `buf` was last read by the P V of the block two back (possibly of the previous unit)
-        if (g >= 2) {
-          if (!__all_sync(0xffffffffu, mbar_wait_bounded(&sm.pv_done[buf], ((g - 2) >> 1) & 1, abort_flag))) {
-            give_up();
-            break;
-          }
-        }
+#if AP_PHASE_TRACE
+        const uint32_t c2b = static_cast<uint32_t>(clock()) + (__float_as_uint(m_run) & 0u);   // after the maximum is known
+#endif
         if (j > 0 && __any_sync(0xffffffffu, grow)) {  // rare: bring O to the new maximum, in tensor memory
           // every MMA issued so far must have finished with O
-          if (!__all_sync(0xffffffffu, mbar_wait_bounded(&sm.pv_done[buf ^ 1], ((g - 1) >> 1) & 1, abort_flag))) {
+          if (!__all_sync(0xffffffffu, mbar_wait_bounded(&sm.pv_done[(g - 1) & 1], ((g - 1) >> 1) & 1, abort_flag))) {
             give_up();
             break;
           }
@@ -421,8 +452,13 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           }
         }
         // ---- probabilities, row sum, bf16 pack into the P buffer
+        AP_CLK(c3);
+        AP_ACC(ph_mx, c2b, c2);
+        AP_ACC(ph_pw, c3, c2b);
         const float neg_m = -m_run;
-        const uint32_t tp = trow + AP_COL_P + buf * (AP_BN / 2);
+        // P overwrites the scores it was computed from (they are in registers by now); the P V that read the
+        // previous contents of this buffer ran before the Q K^T that produced these scores
+        const uint32_t tp = ts;
         float sum0 = 0.f, sum1 = 0.f;
         if (!masked) {
 #pragma unroll
@@ -467,13 +503,17 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
               pl[e >> 1] = pack_bf16(p0 - bf16lo(pk[e >> 1]), p1 - bf16hi(pk[e >> 1]));
             }
             tmem_st_32x16(tp + (c >> 1), pk);
-            tmem_st_32x16(ts + (c >> 1), pl);
+            tmem_st_32x16(ts + AP_BN / 2 + (c >> 1), pl);
           }
         }
+        AP_CLK(c4);
+        AP_ACC(ph_ex, c4, c3);
         tmem_wait_st();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.p_full[buf]);
+        AP_CLK(c5);
+        AP_ACC(ph_st, c5, c4);
         l_run = l_run * alpha + (sum0 + sum1);
       }
       if (dead) break;
@@ -512,9 +552,22 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       g0 += w.nblk;
       ++ui;
     }
+#if AP_PHASE_TRACE
+    if (trace && lane == 0) trace += 8ll * gridDim.x * (warp - 2);   // diagnostic buffer: four rows per CTA
+    if (trace && lane == 0) {
+#else
     if (trace && warp == 2 && lane == 0) {
+#endif
       trace[2] = ui;
       trace[3] = g0;
+#if AP_PHASE_TRACE
+      trace[3] = static_cast<long long>(g0) | (static_cast<long long>(ph_pw) << 32);
+      trace[2] = static_cast<long long>(static_cast<uint32_t>(clock()) - ph_begin) | (static_cast<long long>(ph_st) << 32);
+      trace[4] = ph_s;
+      trace[5] = ph_ld;
+      trace[6] = ph_mx;
+      trace[7] = ph_ex;
+#endif
     }
   }
   tc_fence_before_sync();
@@ -578,7 +631,7 @@ B2_API int b2_attn_prefill(const void* q, const void* k, const void* v, const vo
   if (units > 0x7fffffff) return B2_ERR_UNSUPPORTED;
   a.n_units = static_cast<int>(units);
 
-  const size_t smem = sizeof(AttnPrefillSmem) + 1024;
+  const size_t smem = sizeof(AttnPrefillSmem);
   const bool exp32 = tunable(TUNE_ATTN_PREFILL_EXP16) == 0;
   cudaError_t e = exp32 ? cudaFuncSetAttribute(attn_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                static_cast<int>(smem))
