@@ -50,6 +50,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(LIB_DIR, exist_ok=True)
     nvcc = _nvcc()
     hdr_m = _headers_mtime()
+    stamp = os.path.join(OBJ_DIR, "flags.txt")   # objects built with other flags are stale
+    flags = " ".join(NVCC_FLAGS)
+    if not os.path.exists(stamp) or open(stamp).read() != flags:
+        force = True
     jobs = []
     objs = []
     for src in sources():
@@ -77,6 +81,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 sys.stderr.write(f"[tritonllm_b200.build] {os.path.basename(src)}\n{log}\n")
     if failed:
         raise RuntimeError("nvcc failed; see messages above")
+    with open(stamp, "w") as f:
+        f.write(flags)
     if jobs or force or not os.path.exists(LIB_PATH):
         cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB_PATH, *objs]
         r = subprocess.run(cmd, capture_output=True, text=True)

@@ -90,7 +90,10 @@ struct AttnPrefillSmem {   // placed at the 1024-byte aligned start of dynamic s
   uint64_t kv_empty[AP_STAGES];
   uint64_t s_full[AP_NSP];   // MMA -> softmax: S_j is in buffer j%3
   uint64_t p_full[AP_NSP];   // softmax -> MMA: P_j is in buffer j%3
-  uint64_t pv_done[2];  // MMA -> softmax: O += P_j V_j has completed (slot j&1; needed to rescale or read O)
+  // MMA -> softmax: O += P_j V_j has completed (slot j%3; awaited only to rescale or read O).  Three slots, like the
+  // S buffers: a softmax thread that has seen S_j knows that P_{j-3} V_{j-3} (issued before Q K_j^T) has completed,
+  // i.e. every earlier phase of slot j%3, so its rare parity waits on this slot can never be one phase off.
+  uint64_t pv_done[AP_NSP];
   uint64_t o_free;      // softmax -> MMA: O of the finished unit has been read
   uint32_t tmem_base;
   int abort_flag;
@@ -170,9 +173,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     for (int s = 0; s < 2; ++s) {
       mbar_init(&sm.q_full[s], 1);
       mbar_init(&sm.q_empty[s], 1);
-      mbar_init(&sm.pv_done[s], 1);
     }
     for (int s = 0; s < AP_NSP; ++s) {
+      mbar_init(&sm.pv_done[s], 1);
       mbar_init(&sm.s_full[s], 1);
       mbar_init(&sm.p_full[s], 4);
     }
@@ -336,7 +339,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           for (int k = 0; k < AP_BN / 16; ++k) umma_bf16_ts(tmem + AP_COL_O, tl + 8 * k, dv + 128 * k, IDESC_PV, 1u);
         }
         umma_commit(&sm.kv_empty[s]);
-        umma_commit(&sm.pv_done[cp.g & 1]);
+        umma_commit(&sm.pv_done[cp.g % AP_NSP]);
       }
       __syncwarp();
       // the buffer of this block is free for the block three ahead: the pipe runs it after the MMAs just issued
@@ -437,7 +440,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #endif
         if (j > 0 && __any_sync(0xffffffffu, grow)) {  // rare: bring O to the new maximum, in tensor memory
           // every MMA issued so far must have finished with O
-          if (!__all_sync(0xffffffffu, mbar_wait_bounded(&sm.pv_done[(g - 1) & 1], ((g - 1) >> 1) & 1, abort_flag))) {
+          if (!__all_sync(0xffffffffu, mbar_wait_bounded(&sm.pv_done[(g - 1) % AP_NSP], ((g - 1) / AP_NSP) & 1, abort_flag))) {
             give_up();
             break;
           }
@@ -520,7 +523,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
       // ---- the unit's last P V has completed: read O, hand the accumulator back, store the rows
       const int gl = g0 + w.nblk - 1;
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(&sm.pv_done[gl & 1], (gl >> 1) & 1, abort_flag))) {
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(&sm.pv_done[gl % AP_NSP], (gl / AP_NSP) & 1, abort_flag))) {
         give_up();
         break;
       }
