@@ -31,6 +31,17 @@
 // separate P buffers every block waited some 250 clocks for its S and again for its P buffer; the
 // third buffer takes both waits off the softmax warps' path.  The sink logit joins the denominator at
 // the end.  All waits are bounded.
+//
+// Where a block's ~1650 clocks go (per-phase SM-clock counters of a -DAP_PHASE_TRACE=1 build, T = 8192): 830 in the
+// 64 exponentials per row and their stores (512 would be the special-function unit alone; the other CTA's warp on the
+// same sub-core shares it), ~250 each in the first synchronising instruction after the store burst and in
+// load-latency + row maximum, ~300 in bookkeeping; a unit boundary costs another ~4500 (2400-3000 of it the wait for
+// the last P V to come back through the MMA warp, whose own loop needs ~800 clocks per block to issue eight MMAs and
+// three commits).  Variants measured on the same case and dropped, each within +-2 % or slower: eight softmax warps
+// splitting the columns of a row (exchange of row maxima through shared memory, 25 % slower), fetching the next
+// block's scores before the store drain, packed fp32x2 arithmetic, moving the rescale vote behind the exponentials,
+// requesting the next unit's Q tile three blocks into the current unit, and writing a unit's output one block late
+// (after the first block of the next unit: 5 % slower, the larger loop body spills).
 #include <math_constants.h>
 
 #include <algorithm>
