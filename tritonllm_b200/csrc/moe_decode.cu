@@ -874,6 +874,321 @@ moe_expert_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   }
 }
 
+
+// =====================================================================================================
+// The persistent form of moe_expert_fp4_kernel for 32-token parts.  The one-shot kernel spends about a third of a
+// CTA's life with nothing in flight (launch, barrier and tensor-memory set-up before its first load; accumulator
+// write-out after its last), which is what keeps it near half of the copy bandwidth.  Here a fixed grid of CTAs walks
+// the list of (expert part, weight tile) units, unit w = blockIdx.x + i * gridDim.x with the tile index running
+// fastest, and the ring of stages simply continues from one unit into the next:
+//   warp 0   : TMA producer as before; it also writes the tokens' scale bytes of a stage into the block layout
+//              (64 words per stage, fetched FPP_AHEAD k-blocks ahead through a second cursor over the same stream
+//              of (unit, k-block) positions), so that no epilogue warp is needed inside the k loop;
+//   warp 1   : MMA issuer; one accumulator (64 columns: hi sums | lo sums).  It waits for the epilogue warps to have
+//              copied the previous unit's sums into registers (a few hundred clocks) while the producer already
+//              fills the ring with the next unit's first stages;
+//   warps 2-5: epilogue only: accumulator -> registers, release it, then bias, SwiGLU + requantisation or gate,
+//              staged through 4 KiB of shared memory of their own (the ring is never idle here).
+// Shared memory per stage: 16 KiB padded codes + 8 KiB token tiles + 512 B + 512 B scale blocks.
+// =====================================================================================================
+constexpr int FPP_BN = 32;            // tokens of an expert per unit
+constexpr int FPP_STAGE_BYTES = FP4_A_BYTES + 2 * FPP_BN * 128 + 512 + 512;
+constexpr int FPP_DUMP_BYTES = 4096;
+constexpr int FPP_AHEAD = 4;          // k-blocks the token scale words are fetched ahead
+
+struct __align__(16) MoeFppBarriers {
+  uint64_t full[FP4_MAX_STAGES];     // 2 arrivals: the TMA transaction's and the scale writer's
+  uint64_t empty[FP4_MAX_STAGES];
+  uint64_t acc_full;
+  uint64_t acc_empty;                // 4 arrivals: one per epilogue warp
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct FppUnit {   // one (expert part, weight tile) of the CTA's list
+  int e, row0, n_e, tile;
+  bool valid;
+};
+__device__ __forceinline__ FppUnit fpp_unit(const MoeFp4Args& a, int i, int n_units) {
+  FppUnit u;
+  const int w = static_cast<int>(blockIdx.x) + i * static_cast<int>(gridDim.x);
+  u.valid = w < n_units;
+  if (!u.valid) {
+    u.e = u.row0 = u.n_e = u.tile = 0;
+    return u;
+  }
+  const int item = w / a.tiles;
+  u.tile = w - item * a.tiles;
+  u.e = a.meta->item_expert[item];
+  const int part = a.meta->item_part[item];
+  u.n_e = min(a.meta->counts[u.e] - FPP_BN * part, FPP_BN);
+  u.row0 = a.meta->offsets[u.e] + FPP_BN * part;
+  return u;
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(FP4_THREADS)
+moe_expert_fp4_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_hi,
+                              const __grid_constant__ CUtensorMap tm_lo, const MoeFp4Args a) {
+  overlap_start();
+  overlap_wait();
+  const int n_units = a.meta->n_items * a.tiles;
+  if (static_cast<int>(blockIdx.x) >= n_units) return;
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const int S = a.stages;
+  uint8_t* atile = smem_raw;                                              // S x 16 KiB
+  uint8_t* btile = atile + static_cast<size_t>(S) * FP4_A_BYTES;          // S x (32 hi rows, 32 lo rows) x 128
+  uint8_t* sfa_s = btile + static_cast<size_t>(S) * (2 * FPP_BN * 128);   // S x 512
+  uint8_t* sfb_s = sfa_s + static_cast<size_t>(S) * 512;                  // S x 512
+  uint8_t* dump_s = sfb_s + static_cast<size_t>(S) * 512;                 // 4 KiB
+  MoeFppBarriers& bar = *reinterpret_cast<MoeFppBarriers*>(dump_s + FPP_DUMP_BYTES);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  volatile int* abort_flag = &bar.abort_flag;
+  if ((smem_u32(smem_raw) & 1023u) != 0) {   // the swizzled tiles need this alignment
+    if (tid == 0) atomicOr(a.status, B2_DEV_BAD_INDEX);
+    return;
+  }
+
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&bar.full[s], 2);
+      mbar_init(&bar.empty[s], 1);
+    }
+    mbar_init(&bar.acc_full, 1);
+    mbar_init(&bar.acc_empty, 4);
+    bar.abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_w);
+    tma_prefetch_desc(&tm_hi);
+    tma_prefetch_desc(&tm_lo);
+  }
+  // rows 64..127 of a token scale block are never written again: a harmless scale of 1
+  for (int i = tid; i < S * 128; i += FP4_THREADS) reinterpret_cast<uint32_t*>(sfb_s)[i] = 0x7f7f7f7fu;
+  fence_proxy_async_smem();
+  constexpr int TMEM_COLS = 128;   // accumulator 64, weight scales 4, token scales 4
+  if (warp == 1) tmem_alloc(&bar.tmem_base, TMEM_COLS);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = bar.tmem_base;
+  const int nkb = a.nkb;
+
+  if (warp == 0) {
+    // ===================================== producer + token scale blocks =====================================
+    const bool leader = elect_one();
+    const int sf_stride = 4 * nkb;
+    struct Cur {
+      int i, kb;
+      FppUnit u;
+    };
+    auto next = [&](Cur& c) {
+      if (++c.kb >= nkb) {
+        c.kb = 0;
+        ++c.i;
+        c.u = fpp_unit(a, c.i, n_units);
+      }
+    };
+    // row n2 of the [hi rows; lo rows] token tile: the four scale bytes of one k-block are one word
+    auto load_tsf = [&](const Cur& c, int n2) -> uint32_t {
+      const int term = n2 >= FPP_BN, n = n2 - term * FPP_BN;
+      const uint8_t* sf = term ? a.sf_lo : a.sf_hi;
+      return (c.u.valid && n < c.u.n_e)
+                 ? __ldg(reinterpret_cast<const uint32_t*>(sf + static_cast<size_t>(c.u.row0 + n) * sf_stride) + c.kb)
+                 : 0x7f7f7f7fu;
+    };
+    Cur cur{0, 0, fpp_unit(a, 0, n_units)}, pre = cur;
+    uint32_t nx[FPP_AHEAD][2];
+#pragma unroll
+    for (int d = 0; d < FPP_AHEAD; ++d) {
+      nx[d][0] = load_tsf(pre, lane);
+      nx[d][1] = load_tsf(pre, lane + 32);
+      next(pre);
+    }
+    const int off = lane * 16;   // row r of the block: (r % 32) * 16 + (r / 32) * 4
+    bool ok = true;
+    for (int g = 0; cur.u.valid && ok; ++g) {
+      const int s = g % S, round = g / S;
+      const uint32_t w0 = nx[0][0], w1 = nx[0][1];
+#pragma unroll
+      for (int d = 0; d + 1 < FPP_AHEAD; ++d) {
+        nx[d][0] = nx[d + 1][0];
+        nx[d][1] = nx[d + 1][1];
+      }
+      nx[FPP_AHEAD - 1][0] = load_tsf(pre, lane);
+      nx[FPP_AHEAD - 1][1] = load_tsf(pre, lane + 32);
+      next(pre);
+      if (round > 0) ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar.empty[s], (round - 1) & 1, abort_flag));
+      if (!ok) break;
+      if (leader) {
+        mbar_arrive_expect_tx(&bar.full[s], static_cast<uint32_t>(FP4_A_TX + 512 + 2 * FPP_BN * 128));
+        tma_load_4d(atile + static_cast<size_t>(s) * FP4_A_BYTES, &tm_w, &bar.full[s], cur.kb * FP4_KB, cur.u.tile * MOE_FT,
+                    cur.u.e, 0);
+        bulk_load(sfa_s + s * 512,
+                  a.sfa + ((static_cast<size_t>(cur.u.e) * a.tiles + cur.u.tile) * nkb + cur.kb) * 512, 512, &bar.full[s]);
+        uint8_t* bt = btile + static_cast<size_t>(s) * (2 * FPP_BN * 128);
+        tma_load_2d(bt, &tm_hi, &bar.full[s], cur.kb * FP4_KB, cur.u.row0);
+        tma_load_2d(bt + FPP_BN * 128, &tm_lo, &bar.full[s], cur.kb * FP4_KB, cur.u.row0);   // lo rows follow hi rows
+      }
+      uint8_t* blk = sfb_s + s * 512;
+      *reinterpret_cast<uint32_t*>(blk + off) = w0;
+      *reinterpret_cast<uint32_t*>(blk + off + 4) = w1;
+      fence_proxy_async_smem();   // tcgen05.cp reads the block through the async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar.full[s]);
+      next(cur);
+    }
+    if (leader && !ok) {
+      if (!*abort_flag) atomicOr(a.status, B2_DEV_TIMEOUT_EMPTY);
+      *abort_flag = 1;
+    }
+  } else if (warp == 1) {
+    // ===================================== MMA issuer =====================================
+    const bool leader = elect_one();
+    const uint32_t t_sfa = tmem + 2 * FPP_BN, t_sfb = t_sfa + 4;
+    bool ok = true;
+    int g = 0;
+    for (int i = 0; ok; ++i) {
+      const FppUnit u = fpp_unit(a, i, n_units);
+      if (!u.valid) break;
+      for (int kb = 0; kb < nkb && ok; ++kb, ++g) {
+        const int s = g % S;
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar.full[s], (g / S) & 1, abort_flag));
+        // the previous unit's sums must have left the accumulator
+        if (ok && kb == 0 && i > 0) ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar.acc_empty, (i - 1) & 1, abort_flag));
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint64_t da = umma_desc_k128(smem_u32(atile + static_cast<size_t>(s) * FP4_A_BYTES));
+        const uint64_t db = umma_desc_k128(smem_u32(btile + static_cast<size_t>(s) * (2 * FPP_BN * 128)));
+        if (leader) {
+          tmem_cp_sf_block(t_sfa, umma_desc_sf_block(smem_u32(sfa_s + s * 512)));
+          tmem_cp_sf_block(t_sfb, umma_desc_sf_block(smem_u32(sfb_s + s * 512)));
+#pragma unroll
+          for (int k = 0; k < FP4_KB / 32; ++k)
+            umma_fp4_fp8(tmem, da + 2 * k, db + 2 * k, umma_idesc_fp4_fp8(MOE_FT, 2 * FPP_BN, k, k), t_sfa, t_sfb, (kb | k) != 0);
+          umma_commit(&bar.empty[s]);
+          if (kb == nkb - 1) umma_commit(&bar.acc_full);
+        }
+        __syncwarp();
+      }
+    }
+    if (leader && !ok) {
+      if (!*abort_flag) atomicOr(a.status, B2_DEV_TIMEOUT_MMA);
+      *abort_flag = 1;
+    }
+  } else {
+    // ===================================== epilogue =====================================
+    const int t4 = (warp - 2) * 32 + lane;   // 0..127
+    const int lane_grp = warp & 3;
+    const int fr = lane_grp * 32 + lane;     // feature row of this thread inside the tile
+    const uint32_t trow = tmem + (static_cast<uint32_t>(lane_grp * 32) << 16);
+    __nv_bfloat16* dump = reinterpret_cast<__nv_bfloat16*>(dump_s);
+    constexpr int OUT_F = EPI == MOE_EPI_SWIGLU ? MOE_FT / 2 : MOE_FT;
+    constexpr int PIECES = OUT_F / 8;
+    const int out_n = EPI == MOE_EPI_SWIGLU ? a.N / 2 : a.N;
+    bool ok = true;
+    for (int i = 0; ok; ++i) {
+      const FppUnit u = fpp_unit(a, i, n_units);
+      if (!u.valid) break;
+      const int f = u.tile * MOE_FT + fr;
+      const float bias = f < a.N ? __ldg(a.bias + static_cast<size_t>(u.e) * a.N + f) : 0.f;
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar.acc_full, i & 1, abort_flag));
+      if (!ok) {
+        if (lane == 0 && !*abort_flag) atomicOr(a.status, B2_DEV_TIMEOUT_MMA);
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after_sync();
+      float v[32];
+      {   // columns 0..31 hold the hi term's sums, columns 32..63 the lo term's
+        float w[32];
+        tmem_ld_32x32_nowait(trow, v);
+        tmem_ld_32x32_nowait(trow + FPP_BN, w);
+        tmem_wait_ld();
+#pragma unroll
+        for (int t = 0; t < 32; ++t) v[t] += w[t];
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar.acc_empty);   // the MMA warp may start the next unit
+
+      if constexpr (EPI == MOE_EPI_SWIGLU) {
+#pragma unroll
+        for (int t = 0; t < 32; ++t) {
+          const float xv = v[t] + bias;
+          const float other = __shfl_xor_sync(0xffffffffu, xv, 1);
+          if ((lane & 1) == 0) dump[t * OUT_F + (fr >> 1)] = __float2bfloat16_rn(moe_swiglu(xv, other, a.alpha, a.limit));
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        // straight into the form the second GEMM reads: two block-scaled E4M3 terms per row, one scale byte per 32
+        // features (a tile's 64 features are two whole groups); a thread owns 8 features, a quad a group
+        const int total = u.n_e * PIECES;
+        for (int base = 0; base < total; base += 128) {   // uniform trip count: the shuffles need whole warps
+          const int it = base + t4;
+          const bool live = it < total;
+          const int tok = live ? it / PIECES : 0, pc = it - (it / PIECES) * PIECES;
+          float q[8];
+          if (live) {
+            const uint4 p = *reinterpret_cast<const uint4*>(dump + tok * OUT_F + pc * 8);
+            q[0] = bf16lo(p.x); q[1] = bf16hi(p.x); q[2] = bf16lo(p.y); q[3] = bf16hi(p.y);
+            q[4] = bf16lo(p.z); q[5] = bf16hi(p.z); q[6] = bf16lo(p.w); q[7] = bf16hi(p.w);
+          } else {
+#pragma unroll
+            for (int t = 0; t < 8; ++t) q[t] = 0.f;
+          }
+          uint32_t qb[2][2];
+          uint32_t sbyte[2];
+          moe_quant8(q, qb, sbyte);
+          const int col = u.tile * OUT_F + pc * 8;
+          if (live && col + 8 <= out_n) {
+            const size_t row = static_cast<size_t>(u.row0 + tok);
+            *reinterpret_cast<uint2*>(a.q2_hi + row * a.K2 + col) = make_uint2(qb[0][0], qb[0][1]);
+            *reinterpret_cast<uint2*>(a.q2_lo + row * a.K2 + col) = make_uint2(qb[1][0], qb[1][1]);
+            if ((pc & 3) == 0) {
+              const int gq = col >> 5;
+              a.sf2_hi[row * a.sf2_stride + gq] = static_cast<uint8_t>(sbyte[0]);
+              a.sf2_lo[row * a.sf2_stride + gq] = static_cast<uint8_t>(sbyte[1]);
+              if (gq == a.K2 / 32 - 1)   // groups past K2 (the weights are zero there) get a harmless scale of 1
+                for (int gg = gq + 1; gg < a.sf2_stride; ++gg) {
+                  a.sf2_hi[row * a.sf2_stride + gg] = 127;
+                  a.sf2_lo[row * a.sf2_stride + gg] = 127;
+                }
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // the dump is free for the next unit
+      } else {
+        // 128 features x 16 tokens fill the 4 KiB: two passes
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll
+          for (int t = 0; t < 16; ++t) {
+            const int tok = 16 * half + t;
+            const float gw = tok < u.n_e ? a.meta->gate_of_row[u.row0 + tok] : 0.f;
+            dump[t * OUT_F + fr] = __float2bfloat16_rn((v[tok] + bias) * gw);
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          const int n_here = min(u.n_e - 16 * half, 16);
+          for (int it = t4; it < n_here * PIECES; it += 128) {
+            const int tok = it / PIECES, pc = it - tok * PIECES;
+            const int col = u.tile * OUT_F + pc * 8;
+            if (col + 8 <= out_n)
+              *reinterpret_cast<uint4*>(a.out + static_cast<size_t>(u.row0 + 16 * half + tok) * out_n + col) =
+                  *reinterpret_cast<const uint4*>(dump + tok * OUT_F + pc * 8);
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
 }  // namespace b2
 
 namespace {
@@ -1174,7 +1489,30 @@ B2_API int b2_moe_experts_decode_fp4(const void* x, int64_t ldx, const int16_t* 
     a.status = status;
     const dim3 grid(static_cast<unsigned>(a.tiles), static_cast<unsigned>(rows / tok + n_experts));
     cudaError_t e;
-    if (stage == 0) {
+    if (tok == FPP_BN && tunable(TUNE_MOE_FP4_PERSIST) != 0) {
+      // persistent CTAs over the (expert part, weight tile) list: `per_sm` CTAs per SM share the 8 stages an SM has room for
+      int per_sm = tunable(TUNE_MOE_FP4_PERSIST);
+      per_sm = per_sm >= 4 ? 4 : (per_sm >= 2 ? 2 : 1);
+      a.stages = FP4_MAX_STAGES / per_sm;
+      if (tunable(TUNE_MOE_FP4_STAGES) >= 2 && tunable(TUNE_MOE_FP4_STAGES) <= a.stages) a.stages = tunable(TUNE_MOE_FP4_STAGES);
+      const size_t psmem = static_cast<size_t>(a.stages) * FPP_STAGE_BYTES + FPP_DUMP_BYTES + sizeof(MoeFppBarriers);
+      int dev = 0, sms = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      const long long max_units = static_cast<long long>(a.tiles) * (rows / tok + n_experts);
+      const unsigned pgrid = static_cast<unsigned>(std::min<long long>(static_cast<long long>(per_sm) * sms, max_units));
+      if (stage == 0) {
+        e = cudaFuncSetAttribute(moe_expert_fp4_persist_kernel<MOE_EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(psmem));
+        if (e != cudaSuccess) return static_cast<int>(e);
+        launch_overlapped(moe_expert_fp4_persist_kernel<MOE_EPI_SWIGLU>, dim3(pgrid), dim3(FP4_THREADS), psmem, st, tm_w, tm_hi, tm_lo, a);
+      } else {
+        e = cudaFuncSetAttribute(moe_expert_fp4_persist_kernel<MOE_EPI_GATE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(psmem));
+        if (e != cudaSuccess) return static_cast<int>(e);
+        launch_overlapped(moe_expert_fp4_persist_kernel<MOE_EPI_GATE>, dim3(pgrid), dim3(FP4_THREADS), psmem, st, tm_w, tm_hi, tm_lo, a);
+      }
+    } else if (stage == 0) {
       e = cudaFuncSetAttribute(moe_expert_fp4_kernel<MOE_EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(smem));
       if (e != cudaSuccess) return static_cast<int>(e);
