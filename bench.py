@@ -363,6 +363,8 @@ def decode_run(model, dev, rank: int, batch: int, hbm_peak: float):
     tg.input_token.copy_(prompts[:, -1:])
     out = torch.empty((batch, DECODE_NEW), dtype=torch.int64, device=dev)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(dev.index if dev.index is not None else 0)   # the step runs for seconds: clocks under load
+    sampler.start()
     e0.record()
     for i in range(DECODE_NEW):
         ids = tg._step(True)
@@ -370,6 +372,7 @@ def decode_run(model, dev, rank: int, batch: int, hbm_peak: float):
         out[:, i].copy_(ids)
     e1.record()
     torch.cuda.synchronize()
+    clocks = sampler.stop()
     GEN.check_device_status("decode leg")
     assert int(tg.caches[0].offset.item()) == DECODE_PROMPT - 1 + DECODE_NEW
     assert int(out.min()) >= 0 and int(out.max()) < model.config.vocab_size
@@ -378,7 +381,7 @@ def decode_run(model, dev, rank: int, batch: int, hbm_peak: float):
     del tg
     torch.cuda.empty_cache()
     return {"ms_per_step": ms, "prefill_ms": p0.elapsed_time(p1), "bytes_per_step": nbytes,
-            "gbs": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / hbm_peak, "sequences_per_gpu": batch}
+            "gbs": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / hbm_peak, "sequences_per_gpu": batch, "clocks": clocks}
 
 
 HEADSHARD_T = 8192
@@ -634,7 +637,8 @@ def run_b200(args, rank: int, world: int, local_rank: int):
             dec["weak"] = {"tokens_per_s": DECODE_TOTAL * world / (dw * 1e-3), "ms_per_step": dw, "sequences_per_gpu": DECODE_TOTAL,
                            "total_sequences": DECODE_TOTAL * world, "bytes_per_step_per_gpu": per["bytes_per_step"],
                            "gbs_per_gpu": per["bytes_per_step"] / dw / 1e6, "frac": per["bytes_per_step"] / dw / 1e6 / hbm_peak,
-                           "prefill_tokens_per_s": DECODE_TOTAL * world * (DECODE_PROMPT - 1) / (dwp * 1e-3)}
+                           "prefill_tokens_per_s": DECODE_TOTAL * world * (DECODE_PROMPT - 1) / (dwp * 1e-3),
+                           "clocks": per.get("clocks")}   # rank 0's SM clock during the 256 steps
             if world > 1 and ds < 1e29:
                 per = decode["strong"]
                 dec["strong"] = {"tokens_per_s": DECODE_TOTAL / (ds * 1e-3), "ms_per_step": ds,

@@ -440,9 +440,11 @@ moe_expert_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
 }
 
 // out[t] = sum over the token's slots of y[row_of_slot]   (fp32, slot order)
+// y2 (optional): the rows' second partial sums, when the last GEMM ran with its k range split in two
 __global__ void __launch_bounds__(128) moe_combine_kernel(const __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ out,
                                                           int64_t ld_out, int hidden, int tokens,
-                                                          const MoeMeta* __restrict__ meta) {
+                                                          const MoeMeta* __restrict__ meta,
+                                                          const __nv_bfloat16* __restrict__ y2 = nullptr) {
   overlap_start();
   overlap_wait();
   const int t = blockIdx.x;
@@ -458,6 +460,11 @@ __global__ void __launch_bounds__(128) moe_combine_kernel(const __nv_bfloat16* _
       const uint4 p = __ldg(reinterpret_cast<const uint4*>(y + static_cast<size_t>(rows[k]) * hidden) + i);
       acc[0] += bf16lo(p.x); acc[1] += bf16hi(p.x); acc[2] += bf16lo(p.y); acc[3] += bf16hi(p.y);
       acc[4] += bf16lo(p.z); acc[5] += bf16hi(p.z); acc[6] += bf16lo(p.w); acc[7] += bf16hi(p.w);
+      if (y2) {
+        const uint4 q = __ldg(reinterpret_cast<const uint4*>(y2 + static_cast<size_t>(rows[k]) * hidden) + i);
+        acc[0] += bf16lo(q.x); acc[1] += bf16hi(q.x); acc[2] += bf16lo(q.y); acc[3] += bf16hi(q.y);
+        acc[4] += bf16lo(q.z); acc[5] += bf16hi(q.z); acc[6] += bf16lo(q.w); acc[7] += bf16hi(q.w);
+      }
     }
     uint4 o;
     o.x = pack_bf16(acc[0], acc[1]);
@@ -596,6 +603,8 @@ struct MoeFp4Args {
   int K2, sf2_stride;
   int prefetch;             // k-blocks of weights (codes + scale block) requested into L2 ahead of the ring
   int tok;                  // tokens of one expert per CTA (32 or 64); the rest go to the next CTAs along grid.x
+  int ksplit;               // persistent kernel, gate epilogue: 1, or 2 = a unit is one half of a tile's k range and the
+  int64_t out_half_stride;  //   second half's partial rows go out_half_stride elements further (the combine adds them)
   float alpha, limit;
   int* status;
 };
@@ -910,8 +919,9 @@ struct __align__(16) MoeFppBarriers {
   int abort_flag;
 };
 
-struct FppUnit {   // one (expert part, weight tile) of the CTA's list
+struct FppUnit {   // one (expert part, weight tile[, half of the k range]) of the CTA's list
   int e, row0, n_e, tile;
+  int kh, kb0, kb1;   // which part of the k range, and its k-blocks [kb0, kb1)
   bool valid;
 };
 __device__ __forceinline__ FppUnit fpp_unit(const MoeFp4Args& a, int i, int n_units) {
@@ -919,11 +929,15 @@ __device__ __forceinline__ FppUnit fpp_unit(const MoeFp4Args& a, int i, int n_un
   const int w = static_cast<int>(blockIdx.x) + i * static_cast<int>(gridDim.x);
   u.valid = w < n_units;
   if (!u.valid) {
-    u.e = u.row0 = u.n_e = u.tile = 0;
+    u.e = u.row0 = u.n_e = u.tile = u.kh = u.kb0 = u.kb1 = 0;
     return u;
   }
-  const int item = w / a.tiles;
-  u.tile = w - item * a.tiles;
+  const int per_item = a.tiles * a.ksplit;
+  const int item = w / per_item, rem = w - item * per_item;
+  u.tile = rem / a.ksplit;
+  u.kh = rem - u.tile * a.ksplit;
+  u.kb0 = u.kh * a.nkb / a.ksplit;
+  u.kb1 = (u.kh + 1) * a.nkb / a.ksplit;
   u.e = a.meta->item_expert[item];
   const int part = a.meta->item_part[item];
   u.n_e = min(a.meta->counts[u.e] - FPP_BN * part, FPP_BN);
@@ -937,7 +951,7 @@ moe_expert_fp4_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __
                               const __grid_constant__ CUtensorMap tm_lo, const MoeFp4Args a) {
   overlap_start();
   overlap_wait();
-  const int n_units = a.meta->n_items * a.tiles;
+  const int n_units = a.meta->n_items * a.tiles * a.ksplit;
   if (static_cast<int>(blockIdx.x) >= n_units) return;
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -988,10 +1002,10 @@ moe_expert_fp4_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __
       FppUnit u;
     };
     auto next = [&](Cur& c) {
-      if (++c.kb >= nkb) {
-        c.kb = 0;
+      if (++c.kb >= c.u.kb1) {
         ++c.i;
         c.u = fpp_unit(a, c.i, n_units);
+        c.kb = c.u.kb0;
       }
     };
     // row n2 of the [hi rows; lo rows] token tile: the four scale bytes of one k-block are one word
@@ -1002,7 +1016,9 @@ moe_expert_fp4_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __
                  ? __ldg(reinterpret_cast<const uint32_t*>(sf + static_cast<size_t>(c.u.row0 + n) * sf_stride) + c.kb)
                  : 0x7f7f7f7fu;
     };
-    Cur cur{0, 0, fpp_unit(a, 0, n_units)}, pre = cur;
+    Cur cur{0, 0, fpp_unit(a, 0, n_units)};
+    cur.kb = cur.u.kb0;
+    Cur pre = cur;
     uint32_t nx[FPP_AHEAD][2];
 #pragma unroll
     for (int d = 0; d < FPP_AHEAD; ++d) {
@@ -1056,11 +1072,11 @@ moe_expert_fp4_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __
     for (int i = 0; ok; ++i) {
       const FppUnit u = fpp_unit(a, i, n_units);
       if (!u.valid) break;
-      for (int kb = 0; kb < nkb && ok; ++kb, ++g) {
+      for (int kb = u.kb0; kb < u.kb1 && ok; ++kb, ++g) {
         const int s = g % S;
         ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar.full[s], (g / S) & 1, abort_flag));
         // the previous unit's sums must have left the accumulator
-        if (ok && kb == 0 && i > 0) ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar.acc_empty, (i - 1) & 1, abort_flag));
+        if (ok && kb == u.kb0 && i > 0) ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar.acc_empty, (i - 1) & 1, abort_flag));
         if (!ok) break;
         tc_fence_after_sync();
         const uint64_t da = umma_desc_k128(smem_u32(atile + static_cast<size_t>(s) * FP4_A_BYTES));
@@ -1070,9 +1086,10 @@ moe_expert_fp4_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __
           tmem_cp_sf_block(t_sfb, umma_desc_sf_block(smem_u32(sfb_s + s * 512)));
 #pragma unroll
           for (int k = 0; k < FP4_KB / 32; ++k)
-            umma_fp4_fp8(tmem, da + 2 * k, db + 2 * k, umma_idesc_fp4_fp8(MOE_FT, 2 * FPP_BN, k, k), t_sfa, t_sfb, (kb | k) != 0);
+            umma_fp4_fp8(tmem, da + 2 * k, db + 2 * k, umma_idesc_fp4_fp8(MOE_FT, 2 * FPP_BN, k, k), t_sfa, t_sfb,
+                         ((kb - u.kb0) | k) != 0);
           umma_commit(&bar.empty[s]);
-          if (kb == nkb - 1) umma_commit(&bar.acc_full);
+          if (kb == u.kb1 - 1) umma_commit(&bar.acc_full);
         }
         __syncwarp();
       }
@@ -1096,7 +1113,7 @@ moe_expert_fp4_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __
       const FppUnit u = fpp_unit(a, i, n_units);
       if (!u.valid) break;
       const int f = u.tile * MOE_FT + fr;
-      const float bias = f < a.N ? __ldg(a.bias + static_cast<size_t>(u.e) * a.N + f) : 0.f;
+      const float bias = (f < a.N && u.kh == 0) ? __ldg(a.bias + static_cast<size_t>(u.e) * a.N + f) : 0.f;
       ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar.acc_full, i & 1, abort_flag));
       if (!ok) {
         if (lane == 0 && !*abort_flag) atomicOr(a.status, B2_DEV_TIMEOUT_MMA);
@@ -1178,7 +1195,7 @@ moe_expert_fp4_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __
             const int tok = it / PIECES, pc = it - tok * PIECES;
             const int col = u.tile * OUT_F + pc * 8;
             if (col + 8 <= out_n)
-              *reinterpret_cast<uint4*>(a.out + static_cast<size_t>(u.row0 + 16 * half + tok) * out_n + col) =
+              *reinterpret_cast<uint4*>(a.out + u.kh * a.out_half_stride + static_cast<size_t>(u.row0 + 16 * half + tok) * out_n + col) =
                   *reinterpret_cast<const uint4*>(dump + tok * OUT_F + pc * 8);
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -1316,7 +1333,8 @@ __global__ void __launch_bounds__(128)
 moe_combine_add_norm_kernel(const __nv_bfloat16* __restrict__ y, const MoeMeta* __restrict__ meta,
                             const __nv_bfloat16* __restrict__ residual, int64_t res_stride, const float4* __restrict__ gain,
                             __nv_bfloat16* __restrict__ h_out, int64_t h_stride, __nv_bfloat16* __restrict__ y_out,
-                            int64_t y_stride, int hidden, int tokens, float inv_dim, float eps) {
+                            int64_t y_stride, int hidden, int tokens, float inv_dim, float eps,
+                            const __nv_bfloat16* __restrict__ y2) {
   __shared__ float s_ss[4];
   overlap_start();
   overlap_wait();
@@ -1338,6 +1356,11 @@ moe_combine_add_norm_kernel(const __nv_bfloat16* __restrict__ y, const MoeMeta* 
         const uint4 p = __ldg(reinterpret_cast<const uint4*>(y + static_cast<size_t>(rows[k]) * hidden) + i);
         acc[0] += bf16lo(p.x); acc[1] += bf16hi(p.x); acc[2] += bf16lo(p.y); acc[3] += bf16hi(p.y);
         acc[4] += bf16lo(p.z); acc[5] += bf16hi(p.z); acc[6] += bf16lo(p.w); acc[7] += bf16hi(p.w);
+        if (y2) {
+          const uint4 q = __ldg(reinterpret_cast<const uint4*>(y2 + static_cast<size_t>(rows[k]) * hidden) + i);
+          acc[0] += bf16lo(q.x); acc[1] += bf16hi(q.x); acc[2] += bf16lo(q.y); acc[3] += bf16hi(q.y);
+          acc[4] += bf16lo(q.z); acc[5] += bf16hi(q.z); acc[6] += bf16lo(q.w); acc[7] += bf16hi(q.w);
+        }
       }
       // the MoE output is a bf16 tensor; the residual add rounds once more
       const uint4 d = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]),
@@ -1373,6 +1396,30 @@ moe_combine_add_norm_kernel(const __nv_bfloat16* __restrict__ y, const MoeMeta* 
 }  // namespace b2
 
 // ------------------------------------------------------------------------------- FP4 tensor-core path
+namespace {
+// How b2_moe_experts_decode_fp4 runs under the current tuning knobs; b2_moe_combine_add_rmsnorm must agree with it on
+// where the last GEMM's second partial rows are.
+struct MoeFp4Plan {
+  int tok;      // tokens of an expert per CTA
+  int per_sm;   // persistent kernel: CTAs per SM; 0: the one-shot kernel
+  int ksplit;   // last GEMM: parts of the k range (2: each weight tile is two units and every row has two partial sums)
+};
+MoeFp4Plan moe_fp4_plan(int64_t tokens, int intermediate) {
+  using namespace b2;
+  MoeFp4Plan p{32, 0, 1};
+  if (tunable(TUNE_MOE_FP4_TOK) == 32 || tunable(TUNE_MOE_FP4_TOK) == 64) p.tok = tunable(TUNE_MOE_FP4_TOK);
+  const int ps = tunable(TUNE_MOE_FP4_PERSIST);
+  if (p.tok == FPP_BN && ps != 0) {
+    p.per_sm = ps >= 4 ? 4 : (ps >= 2 ? 2 : 1);
+    // two halves pay off while the last GEMM's units are fewer than two rounds of CTAs (measured: 32 tokens 114 -> 110 us,
+    // 2048 tokens 584 -> 607 us); a half must hold at least two k-blocks
+    const int nkb = (intermediate + FP4_KB - 1) / FP4_KB;
+    p.ksplit = (tunable(TUNE_MOE_FP4_KSPLIT) == 1 || nkb < 4 || tokens > 512) ? 1 : 2;
+  }
+  return p;
+}
+}  // namespace
+
 B2_API size_t b2_moe_fp4_workspace_bytes(int64_t tokens, int hidden, int intermediate) {
   if (tokens <= 0 || hidden <= 0 || intermediate <= 0) return 0;
   const size_t rows = static_cast<size_t>(tokens) * b2::MOE_TOPK;
@@ -1431,8 +1478,10 @@ B2_API int b2_moe_experts_decode_fp4(const void* x, int64_t ldx, const int16_t* 
   const int bn_all = ((T < MOE_MAX_TOKENS ? T : MOE_MAX_TOKENS) + 31) & ~31;
   // 32 tokens of an expert per CTA: two stages, four CTAs per SM.  With the item list this beats 64 tokens (three
   // stages, two CTAs per SM) at every size measured (256 tokens: 166 against 183 us; 2048: 769 against 786 us)
-  int tok = 32;
-  if (tunable(TUNE_MOE_FP4_TOK) == 32 || tunable(TUNE_MOE_FP4_TOK) == 64) tok = tunable(TUNE_MOE_FP4_TOK);
+  const MoeFp4Plan plan = moe_fp4_plan(tokens, intermediate);
+  const int tok = plan.tok;
+  // the first GEMM's input rows are dead when the last GEMM runs: its second partial rows go there
+  __nv_bfloat16* ybuf2 = reinterpret_cast<__nv_bfloat16*>(q_hi);
   const int bn_max = bn_all < tok ? bn_all : tok;   // tokens of one expert per CTA; more go to further items of the list
   launch_overlapped(moe_route_kernel, dim3(1), dim3(1024), 0, st, topk_idx, topk_w, static_cast<int>(T), n_experts, meta, status, tok);
   const int stage_bytes = FP4_A_BYTES + 2 * bn_max * 128 + 512 + 2048;
@@ -1488,23 +1537,24 @@ B2_API int b2_moe_experts_decode_fp4(const void* x, int64_t ldx, const int16_t* 
     a.stages = stages;
     a.sf_col = 2 * bn_max;
     a.tok = tok;
+    a.ksplit = stage == 1 ? plan.ksplit : 1;
+    a.out_half_stride = ybuf2 - ybuf;
     a.prefetch = tunable(TUNE_MOE_PREFETCH) < 0 ? 0 : (tunable(TUNE_MOE_PREFETCH) > 32 ? 32 : tunable(TUNE_MOE_PREFETCH));
     a.alpha = alpha;
     a.limit = limit;
     a.status = status;
     const dim3 grid(static_cast<unsigned>(a.tiles), static_cast<unsigned>(rows / tok + n_experts));
     cudaError_t e;
-    if (tok == FPP_BN && tunable(TUNE_MOE_FP4_PERSIST) != 0) {
+    if (plan.per_sm > 0) {
       // persistent CTAs over the (expert part, weight tile) list: `per_sm` CTAs per SM share the 8 stages an SM has room for
-      int per_sm = tunable(TUNE_MOE_FP4_PERSIST);
-      per_sm = per_sm >= 4 ? 4 : (per_sm >= 2 ? 2 : 1);
+      const int per_sm = plan.per_sm;
       a.stages = FP4_MAX_STAGES / per_sm;
       if (tunable(TUNE_MOE_FP4_STAGES) >= 2 && tunable(TUNE_MOE_FP4_STAGES) <= a.stages) a.stages = tunable(TUNE_MOE_FP4_STAGES);
       const size_t psmem = static_cast<size_t>(a.stages) * FPP_STAGE_BYTES + FPP_DUMP_BYTES + sizeof(MoeFppBarriers);
       int dev = 0, sms = 0;
       cudaGetDevice(&dev);
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-      const long long max_units = static_cast<long long>(a.tiles) * (rows / tok + n_experts);
+      const long long max_units = static_cast<long long>(a.tiles) * a.ksplit * (rows / tok + n_experts);
       const unsigned pgrid = static_cast<unsigned>(std::min<long long>(static_cast<long long>(per_sm) * sms, max_units));
       if (stage == 0) {
         e = cudaFuncSetAttribute(moe_expert_fp4_persist_kernel<MOE_EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1532,7 +1582,9 @@ B2_API int b2_moe_experts_decode_fp4(const void* x, int64_t ldx, const int16_t* 
     if (rc != B2_OK) return rc;
   }
   if (out)
-    launch_overlapped(moe_combine_kernel, dim3(T), dim3(128), 0, st, ybuf, static_cast<__nv_bfloat16*>(out), ld_out, hidden, static_cast<int>(T), meta);
+    launch_overlapped(moe_combine_kernel, dim3(T), dim3(128), 0, st, static_cast<const __nv_bfloat16*>(ybuf), static_cast<__nv_bfloat16*>(out),
+                      ld_out, hidden, static_cast<int>(T), static_cast<const MoeMeta*>(meta),
+                      static_cast<const __nv_bfloat16*>(plan.ksplit == 2 ? ybuf2 : nullptr));
   return launch_status();
 }
 
@@ -1554,10 +1606,12 @@ B2_API int b2_moe_combine_add_rmsnorm(const void* workspace, size_t workspace_by
   const uint8_t* ws = static_cast<const uint8_t*>(workspace);
   const MoeMeta* meta = reinterpret_cast<const MoeMeta*>(ws);
   ws += moe_align(sizeof(MoeMeta)) + moe_align(rows * hidden * 2) + moe_align(rows * intermediate * 2);
+  const __nv_bfloat16* y2 =
+      moe_fp4_plan(tokens, intermediate).ksplit == 2 ? reinterpret_cast<const __nv_bfloat16*>(ws + moe_align(rows * hidden * 2)) : nullptr;
   launch_overlapped(moe_combine_add_norm_kernel, dim3(static_cast<unsigned>(tokens)), dim3(128), 0,
                     static_cast<cudaStream_t>(stream), reinterpret_cast<const __nv_bfloat16*>(ws), meta,
                     static_cast<const __nv_bfloat16*>(residual), residual_stride, reinterpret_cast<const float4*>(gain),
                     static_cast<__nv_bfloat16*>(h_out), h_stride, static_cast<__nv_bfloat16*>(y_out), y_stride, hidden,
-                    static_cast<int>(tokens), 1.0f / static_cast<float>(hidden), eps);
+                    static_cast<int>(tokens), 1.0f / static_cast<float>(hidden), eps, y2);
   return launch_status();
 }
