@@ -378,6 +378,8 @@ def _parser():
                     help="time the reference's own Triton kernel for the case instead (attn_decode, attn_prefill, moe_decode, "
                          "rmsnorm, rope, qkv_decode, oproj_decode); needs a TritonLLM checkout and triton")
     ap.add_argument("--tune", action="append", default=[], help="name=value tuning knob (b2_set_tunable)")
+    ap.add_argument("--phase-trace", action="store_true",
+                    help="attn_prefill: also print the softmax warps' per-phase clock counters (diagnostic build of the library)")
     return ap
 
 
@@ -448,6 +450,37 @@ def run_case(a) -> dict:
             "algorithmic_flops": flops, **_tensor_fields(flops, us)}
 
 
+def attn_prefill_phases(a) -> dict:
+    """Per-phase SM-clock counters of the prefill attention kernel's softmax warps, per 64-key block, averaged over the
+    CTAs.  They exist only in a diagnostic build of the library
+    (`TRITONLLM_B200_NVCC_FLAGS=-DAP_PHASE_TRACE=1 python -m tritonllm_b200.build`); a plain build leaves them at zero."""
+    import ctypes as C
+    fn = build_case("attn_prefill", a)[0]
+    fn()
+    torch.cuda.synchronize()
+    rows = 4 * 1024   # four softmax warps per CTA, 8 slots per row
+    buf = torch.zeros(rows * 8, dtype=torch.int64, device="cuda")
+    _lib.call("b2_set_trace_buffer", C.c_void_p(buf.data_ptr()), C.c_size_t(buf.numel() * 8))
+    try:
+        fn()
+        torch.cuda.synchronize()
+    finally:
+        _lib.call("b2_set_trace_buffer", C.c_void_p(0), C.c_size_t(0))
+    t = buf.view(rows, 8).cpu()
+    t = t[(t[:, 3] & 0xffffffff) > 0]
+    if len(t) == 0 or int(t[:, 4:8].sum()) == 0:
+        return {"phases": None, "note": "the library was not built with -DAP_PHASE_TRACE=1"}
+    blocks = (t[:, 3] & 0xffffffff).double()
+    per = lambda col: round(float((col.double() / blocks).mean()), 1)  # noqa: E731
+    total, drain = t[:, 2] & 0xffffffff, t[:, 2] >> 32
+    named = {"wait_for_S": t[:, 4], "tensor_memory_load_issue": t[:, 5], "load_latency_and_row_max": t[:, 6],
+             "rescale_vote_and_P_buffer_wait": t[:, 3] >> 32, "exponentials_pack_stores": t[:, 7], "store_drain_and_arrive": drain}
+    out = {k: per(v) for k, v in named.items()}
+    out["total_per_block"] = per(total)
+    out["bookkeeping_and_unit_ends"] = round(out["total_per_block"] - sum(v for k, v in out.items() if k != "total_per_block"), 1)
+    return {"phases": out, "warps": len(t), "blocks_per_cta": round(float(blocks.mean()), 1), "unit": "SM clocks per 64-key block"}
+
+
 def main():
     a = _parser().parse_args()
     assert torch.cuda.is_available(), "cases need a CUDA device"
@@ -460,7 +493,10 @@ def main():
     if a.case == "decode_stack":
         decode_stack(a)
         return
-    print(json.dumps(run_case(a)))
+    rec = run_case(a)
+    if a.case == "attn_prefill" and a.phase_trace:
+        rec.update(attn_prefill_phases(a))
+    print(json.dumps(rec))
 
 
 if __name__ == "__main__":

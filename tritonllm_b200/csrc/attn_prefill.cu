@@ -77,9 +77,11 @@ struct AttnPrefillArgs {
   long long* trace;     // optional [CTA][8] (b2_set_trace_buffer): start ns, end ns, units, blocks
 };
 
-// Diagnostic build (-DAP_PHASE_TRACE=1): softmax warp 2 of every CTA adds up the SM clocks it spends per phase of a
-// block into trace slots 4..7 (wait for S, tensor-memory load, maximum + wait for the P buffer, exponentials + stores)
-// and slot 2 (its whole loop in the low 32 bits, store drain + arrive in the high 32 bits).
+// Diagnostic build (-DAP_PHASE_TRACE=1): every softmax warp adds up the SM clocks it spends per phase of a block; the
+// trace buffer then needs four rows of 8 slots per CTA, row = (warp - 2) * gridDim.x + blockIdx.x: slot 2 = the warp's
+// whole loop (low 32 bits) and store drain + arrive (high), slot 3 = blocks (low) and rescale vote / P wait (high),
+// slots 4..7 = wait for S, tensor-memory load issue, load latency + row maximum, exponentials + pack + stores.
+// `cases.py attn_prefill --phase-trace` prints them.
 #ifndef AP_PHASE_TRACE
 #define AP_PHASE_TRACE 0
 #endif
