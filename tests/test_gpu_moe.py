@@ -308,6 +308,31 @@ def test_moe_prefill_real_dims_against_the_oracle_and_the_decode_sized_kernel():
     assert_parity(_oracle(x[sel], vals[sel], idx[sel], w1, w2), out[sel], "prompt-sized MoE, sampled tokens vs oracle")
 
 
+def test_moe_prefill_resident_expansion_is_the_same_computation():
+    """With a budget, the bf16 expansion of an expert pair is made once and kept; results do not change."""
+    ops = _ops()
+    E, H, I, T = 8, 768, 768, 640
+    gen = torch.Generator().manual_seed(4702)
+    x = torch.randn(T, H, generator=gen).bfloat16()
+    vals, idx = _routing(gen, T, E)
+    p1, p2 = _packed(_random_experts(gen, E, 2 * I, H)), _packed(_random_experts(gen, E, H, I))
+    args = (x.cuda(), vals.cuda(), idx.cuda(), p1, p2)
+    plain = ops.moe_experts_prefill(*args).cpu()
+    ops.set_expanded_expert_budget(1 << 30)
+    try:
+        first = ops.moe_experts_prefill(*args).cpu()
+        assert getattr(p1, "_expanded", None) is not None
+        second = ops.moe_experts_prefill(*args).cpu()          # no expansion this time
+        ops.drop_expanded_experts(p1)
+        assert p1._expanded is None
+    finally:
+        ops.set_expanded_expert_budget(0)
+        ops.drop_expanded_experts()
+    torch.cuda.synchronize()
+    assert torch.equal(plain.view(torch.int16), first.view(torch.int16))
+    assert torch.equal(plain.view(torch.int16), second.view(torch.int16))
+
+
 def test_moe_prefill_config4_shape_and_edges():
     """BASELINE config 4's token count and expert count (16384 tokens, 128 experts, hidden 2880): every token of the
     grouped-GEMM path against the decode-sized kernel run in blocks, plus experts without tokens."""

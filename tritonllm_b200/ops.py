@@ -771,6 +771,32 @@ def _moe_from_reference(x, wg, w1, w1_mx, w2, w2_mx, bg, b1, b2, experts_per_tok
 
 
 _moe_prefill_ws: dict = {}
+_expanded_budget = 0          # bytes per device that resident bf16 copies of expert weights may take (0: none)
+_expanded_used: dict = {}     # device -> bytes taken so far
+
+
+def set_expanded_expert_budget(nbytes: int) -> None:
+    """Memory for speed on the prompt path: up to `nbytes` of device memory (per device) may hold the bf16 expansion
+    of MXFP4 expert weights from one `moe_experts_prefill` call to the next (3.2 GB per gpt-oss-20b layer, 38 GB for
+    the model), which takes the per-call expansion (0.6 ms of 1.7 ms at 8192 tokens) out of every later call.  The
+    copy belongs to the `ExpertWeightsFp4` pair it was made from and is not refreshed if their tensors are
+    overwritten in place: call `drop_expanded_experts` then.  0 (the default): one shared scratch, expanded per call."""
+    global _expanded_budget
+    _expanded_budget = int(nbytes)
+
+
+def drop_expanded_experts(w1=None) -> None:
+    """Forgets the resident bf16 copy made for `w1` (or counts every copy as released when w1 is None; the copies
+    themselves die with their weight objects)."""
+    if w1 is None:
+        _expanded_used.clear()
+        return
+    hit = getattr(w1, "_expanded", None)
+    if hit is not None:
+        dev = hit[0].device
+        _expanded_used[dev] = _expanded_used.get(dev, 0) - hit[0].numel() * 2 - hit[1].numel() * 2
+        w1._expanded = None
+
 PREFILL_MOE_MIN_TOKENS = 2049    # from here on the grouped GEMM (tokens as M rows) beats the decode-sized kernel
 
 
@@ -800,8 +826,19 @@ def moe_experts_prefill(x, topk_vals, topk_idx, w1, w2, alpha=1.702, limit=7.0):
                torch.empty((e * hidden, inter), dtype=_BF16, device=x.device))
         _moe_prefill_ws[key] = hit
     ws, w1b, w2b = hit
-    _lib.call("b2_moe_upcast_packed", w1.codes.data_ptr(), w1.sf.data_ptr(), w1b.data_ptr(), e, 2 * inter, hidden, _stream())
-    _lib.call("b2_moe_upcast_packed", w2.codes.data_ptr(), w2.sf.data_ptr(), w2b.data_ptr(), e, hidden, inter, _stream())
+    resident = getattr(w1, "_expanded", None)
+    if resident is not None and resident[2] is w2:
+        w1b, w2b = resident[0], resident[1]            # expanded by an earlier call
+    else:
+        size = (w1b.numel() + w2b.numel()) * 2
+        keep = _expanded_budget > 0 and _expanded_used.get(x.device, 0) + size <= _expanded_budget
+        if keep:                                       # this pair gets a copy of its own, made once
+            w1b, w2b = torch.empty_like(w1b), torch.empty_like(w2b)
+        _lib.call("b2_moe_upcast_packed", w1.codes.data_ptr(), w1.sf.data_ptr(), w1b.data_ptr(), e, 2 * inter, hidden, _stream())
+        _lib.call("b2_moe_upcast_packed", w2.codes.data_ptr(), w2.sf.data_ptr(), w2b.data_ptr(), e, hidden, inter, _stream())
+        if keep:
+            w1._expanded = (w1b, w2b, w2)
+            _expanded_used[x.device] = _expanded_used.get(x.device, 0) + size
     _lib.call("b2_moe_experts_prefill", x.data_ptr(), x.stride(0), topk_idx.data_ptr(), topk_vals.data_ptr(), w1b.data_ptr(),
               w1.bias.data_ptr(), w2b.data_ptr(), w2.bias.data_ptr(), out.data_ptr(), out.stride(0), ws.data_ptr(), ws.numel(),
               t, e, hidden, inter, float(alpha), float(limit), _stream())
