@@ -82,10 +82,16 @@ def test_rope(ops, tables, B, T, offset):
     assert_parity(kr, kd, "rope k")
     # fused multiply-add on the GPU vs separate roundings in torch: one bf16 step, except where
     # x1*cos - x2*sin cancels to a value far smaller than its terms
-    for ref, got in ((qr, qd), (kr, kd)):
+    for src, ref, got in ((q, qr, qd), (k, kr, kd)):
         ulp = bf16_ulp_diff(ref, got)
         assert (ulp > 1).float().mean() < 1e-4 and (ulp > 0).float().mean() < 0.02
         torch.testing.assert_close(got.cpu().float(), ref.float(), atol=2e-3, rtol=2 ** -7)
+        # which elements exceed one step: only those where the two products cancel, i.e. the result is at least
+        # eight times smaller than the larger input of its (j, j + 32) pair
+        big = torch.maximum(src[..., :32].abs(), src[..., 32:].abs()).float().repeat(1, 1, 1, 2)
+        off = ulp > 1
+        assert bool((ref.float().abs()[off] * 8 <= big[off]).all()), \
+            f"{int(off.sum())} elements differ by more than one bf16 step; not all of them are cancellations"
 
 
 def test_rope_golden(ops, tables):

@@ -292,9 +292,9 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         }
       }
     }
-  } else if (warp >= 2 && !*abort_flag) {
+  } else if (a.epi != EPI_LOGITS && !*abort_flag) {
     // ================================ reduce across the cluster + epilogue ================================
-    const int e = (warp - 2) * 32 + lane;  // 0..127
+    const int e = tid;  // all six warps: the producer and the MMA warp have nothing left to do
     long long offset = 0, pos = 0;
     bool offset_ok = true;
     const bool per_seq = a.epi == EPI_QKV && (a.offset_stride != 0 || a.block_table != nullptr);
@@ -307,9 +307,9 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     }
     // items = (sequence, four consecutive row pairs), rows fastest: the 16 lanes of a sequence read 2 x 256
     // contiguous bytes of each slice's dump and write runs of 64-128 contiguous bytes of the output row;
-    // this CTA takes every KS-th group of 128 items
+    // this CTA takes every KS-th group of 192 items
     const int items = bn * 16;
-    for (int it = rank * 128 + e; it < items; it += KS * 128) {
+    for (int it = rank * SK_THREADS + e; it < items; it += KS * SK_THREADS) {
       const int c = it >> 4, qd = it & 15;
       const int b = b0 + c;
       if (b >= a.batch) continue;

@@ -57,9 +57,9 @@ struct MoeMeta {          // lives at the start of the workspace
 };
 
 // ------------------------------------------------------------------------------------------- routing
-__global__ void __launch_bounds__(1024) moe_route_kernel(const int16_t* __restrict__ topk_idx,
-                                                         const float* __restrict__ topk_w, int tokens, int n_experts,
-                                                         MoeMeta* meta, int* status, int tok) {
+// The routing work of one CTA (any block size that is a multiple of 32).
+__device__ __forceinline__ void moe_route_body(const int16_t* __restrict__ topk_idx, const float* __restrict__ topk_w,
+                                               int tokens, int n_experts, MoeMeta* meta, int* status, int tok) {
   __shared__ uint32_t mask[MOE_MAX_EXPERTS][MOE_MAX_TOKENS / 32];  // which tokens chose expert e
   __shared__ int offs[MOE_MAX_EXPERTS + 1];
   const int tid = threadIdx.x;
@@ -129,6 +129,12 @@ __global__ void __launch_bounds__(1024) moe_route_kernel(const int16_t* __restri
     }
     meta->row_of_slot[sl] = row;
   }
+}
+
+__global__ void __launch_bounds__(1024) moe_route_kernel(const int16_t* __restrict__ topk_idx,
+                                                         const float* __restrict__ topk_w, int tokens, int n_experts,
+                                                         MoeMeta* meta, int* status, int tok) {
+  moe_route_body(topk_idx, topk_w, tokens, n_experts, meta, status, tok);
 }
 
 // one CTA per routed row: x[token] -> xs[row]
@@ -484,8 +490,8 @@ __global__ void __launch_bounds__(128) moe_combine_kernel(const __nv_bfloat16* _
 // accumulated into the same fp32 accumulator.
 //   weights   codes [E][N][Kp/2], Kp = K rounded up to 128, zero padded (TMA type 16U4_ALIGN16B needs it);
 //             scales as ready-made 512-byte blocks [E][N/128][Kp/128][r%32][r/32][group%4]
-//   moe_quant_kernel   bf16 rows -> hi / lo E4M3 rows and their scale bytes (the first call also gathers the tokens' rows
-//             into expert-sorted order)
+//   moe_route_quant_kernel   the routing (last CTA) and, one CTA per routed (token, slot) pair, the token's bf16 row ->
+//             hi / lo E4M3 rows and their scale bytes at the pair's place in the expert-sorted order (the gather)
 //   moe_expert_fp4_kernel   warp 0: TMA (codes 8 KiB -> padded 16 KiB tile, the scale block, the tokens' hi and lo
 //             tiles); warps 2-5: per stage, the tokens' scale bytes into the same block layout, later the epilogue;
 //             warp 1: tcgen05.cp of the scale blocks into tensor memory, then 4 MMAs (K = 32 each) whose N covers the
@@ -536,18 +542,11 @@ __device__ __forceinline__ void moe_quant8(float (&v)[8], uint32_t (&qb)[2][2], 
 
 // One CTA per row; a thread owns 8 consecutive elements, four threads one 32-element group.  With `meta` the CTA is
 // a routed (token, slot) pair: it reads the token's row and writes the row of the expert-sorted order (the gather).
-__global__ void __launch_bounds__(128) moe_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, int K,
-                                                        uint8_t* __restrict__ q_hi, uint8_t* __restrict__ q_lo,
-                                                        uint8_t* __restrict__ sf_hi, uint8_t* __restrict__ sf_lo, int sf_stride,
-                                                        const MoeMeta* __restrict__ meta) {
-  overlap_start();
-  overlap_wait();
-  int row = blockIdx.x, src_row = blockIdx.x;
-  if (meta) {
-    row = meta->row_of_slot[blockIdx.x];
-    src_row = blockIdx.x / MOE_TOPK;
-    if (row < 0) return;
-  }
+// Row src_row of x -> row `row` of the two E4M3 terms and their scale bytes (the whole CTA works on the row).
+__device__ __forceinline__ void moe_quant_row(const __nv_bfloat16* __restrict__ x, int64_t ldx, int K,
+                                              uint8_t* __restrict__ q_hi, uint8_t* __restrict__ q_lo,
+                                              uint8_t* __restrict__ sf_hi, uint8_t* __restrict__ sf_lo, int sf_stride,
+                                              int row, int src_row) {
   const int chunks = K / 8;
   const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(src_row) * ldx);
   for (int base = 0; base < chunks; base += blockDim.x) {   // uniform trip count: the shuffles need whole warps
@@ -579,6 +578,63 @@ __global__ void __launch_bounds__(128) moe_quant_kernel(const __nv_bfloat16* __r
     sf_hi[static_cast<size_t>(row) * sf_stride + g] = 127;
     sf_lo[static_cast<size_t>(row) * sf_stride + g] = 127;
   }
+}
+
+// One CTA per routed (token, slot) pair, after the routing kernel: the token's row -> the pair's row of the sorted order.
+__global__ void __launch_bounds__(128) moe_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, int K,
+                                                        uint8_t* __restrict__ q_hi, uint8_t* __restrict__ q_lo,
+                                                        uint8_t* __restrict__ sf_hi, uint8_t* __restrict__ sf_lo, int sf_stride,
+                                                        const MoeMeta* __restrict__ meta) {
+  overlap_start();
+  overlap_wait();
+  const int row = meta->row_of_slot[blockIdx.x];
+  if (row < 0) return;
+  moe_quant_row(x, ldx, K, q_hi, q_lo, sf_hi, sf_lo, sf_stride, row, blockIdx.x / MOE_TOPK);
+}
+
+// Routing and the first quantise / gather pass in one launch: CTA `slots` (the last) does the routing for the kernels
+// that follow; CTA sl < slots quantises the row of routed pair sl and finds its place in the expert-sorted order by
+// itself: (tokens' distinct valid experts below e) + (earlier tokens that chose e), which is what the routing CTA
+// writes into row_of_slot at the same time.
+constexpr int MOE_RQ_THREADS = 256;
+__global__ void __launch_bounds__(MOE_RQ_THREADS)
+moe_route_quant_kernel(const int16_t* __restrict__ topk_idx, const float* __restrict__ topk_w, int tokens, int n_experts,
+                       MoeMeta* meta, int* status, int tok, const __nv_bfloat16* __restrict__ x, int64_t ldx, int K,
+                       uint8_t* __restrict__ q_hi, uint8_t* __restrict__ q_lo, uint8_t* __restrict__ sf_hi,
+                       uint8_t* __restrict__ sf_lo, int sf_stride) {
+  const int slots = tokens * MOE_TOPK;
+  if (static_cast<int>(blockIdx.x) == slots) {
+    moe_route_body(topk_idx, topk_w, tokens, n_experts, meta, status, tok);
+    return;
+  }
+  overlap_start();
+  overlap_wait();
+  __shared__ int s_cnt[MOE_RQ_THREADS / 32];
+  const int sl = blockIdx.x, t = sl / MOE_TOPK;
+  const int e = topk_idx[sl];
+  if (e < 0 || e >= n_experts) return;   // flagged by the routing CTA; the pair has no row
+  int cnt = 0;
+  for (int u = threadIdx.x; u < tokens; u += blockDim.x) {
+    const uint2 raw = __ldg(reinterpret_cast<const uint2*>(topk_idx) + u);
+    const int id[4] = {static_cast<int16_t>(raw.x & 0xffffu), static_cast<int16_t>(raw.x >> 16),
+                       static_cast<int16_t>(raw.y & 0xffffu), static_cast<int16_t>(raw.y >> 16)};
+#pragma unroll
+    for (int k = 0; k < MOE_TOPK; ++k) {
+      const int ek = id[k];
+      if (ek < 0 || ek >= n_experts) continue;
+      bool first = true;   // a repeated id counts once, as in the routing CTA's bit masks
+#pragma unroll
+      for (int j = 0; j < k; ++j) first = first && id[j] != ek;
+      if (first && (ek < e || (ek == e && u < t))) ++cnt;
+    }
+  }
+  cnt = __reduce_add_sync(0xffffffffu, cnt);
+  if ((threadIdx.x & 31) == 0) s_cnt[threadIdx.x >> 5] = cnt;
+  __syncthreads();
+  int row = 0;
+#pragma unroll
+  for (int w = 0; w < MOE_RQ_THREADS / 32; ++w) row += s_cnt[w];
+  moe_quant_row(x, ldx, K, q_hi, q_lo, sf_hi, sf_lo, sf_stride, row, t);
 }
 
 constexpr int FP4_KB = 128;                       // K elements per pipeline stage (4 MMA steps of 32)
@@ -1483,7 +1539,18 @@ B2_API int b2_moe_experts_decode_fp4(const void* x, int64_t ldx, const int16_t* 
   // the first GEMM's input rows are dead when the last GEMM runs: its second partial rows go there
   __nv_bfloat16* ybuf2 = reinterpret_cast<__nv_bfloat16*>(q_hi);
   const int bn_max = bn_all < tok ? bn_all : tok;   // tokens of one expert per CTA; more go to further items of the list
-  launch_overlapped(moe_route_kernel, dim3(1), dim3(1024), 0, st, topk_idx, topk_w, static_cast<int>(T), n_experts, meta, status, tok);
+  const int nkb1 = (hidden + FP4_KB - 1) / FP4_KB;
+  if (T <= 512) {
+    // routing and the first quantise / gather pass in one launch (the last CTA routes, the others place their rows
+    // themselves by a scan of the top-k table, which stops paying above a few hundred tokens: 2048 tokens 593 -> 640 us)
+    launch_overlapped(moe_route_quant_kernel, dim3(rows + 1), dim3(MOE_RQ_THREADS), 0, st, topk_idx, topk_w, static_cast<int>(T),
+                      n_experts, meta, status, tok, static_cast<const __nv_bfloat16*>(x), ldx, hidden, q_hi, q_lo, sf_hi, sf_lo,
+                      4 * nkb1);
+  } else {
+    launch_overlapped(moe_route_kernel, dim3(1), dim3(1024), 0, st, topk_idx, topk_w, static_cast<int>(T), n_experts, meta, status, tok);
+    launch_overlapped(moe_quant_kernel, dim3(rows), dim3(128), 0, st, static_cast<const __nv_bfloat16*>(x), ldx, hidden, q_hi, q_lo,
+                      sf_hi, sf_lo, 4 * nkb1, static_cast<const MoeMeta*>(meta));
+  }
   const int stage_bytes = FP4_A_BYTES + 2 * bn_max * 128 + 512 + 2048;
   // small token tiles: two stages per CTA and four CTAs per SM (start-up and write-out of one CTA hide behind the
   // streaming of the others) beat four stages and two CTAs; larger tiles are limited to two CTAs by tensor memory
@@ -1496,10 +1563,7 @@ B2_API int b2_moe_experts_decode_fp4(const void* x, int64_t ldx, const int16_t* 
     const int K = stage == 0 ? hidden : intermediate;
     const int Kp = (K + FP4_KB - 1) / FP4_KB * FP4_KB;
     const int nkb = Kp / FP4_KB;
-    // the rows of this stage as two block-scaled E4M3 terms; the first stage gathers the tokens' rows on the way
-    if (stage == 0)
-      launch_overlapped(moe_quant_kernel, dim3(rows), dim3(128), 0, st, static_cast<const __nv_bfloat16*>(x), ldx, K, q_hi, q_lo, sf_hi, sf_lo, 4 * nkb, meta);
-    // (the second GEMM's rows were quantised by the first GEMM's epilogue)
+    // (the first GEMM's rows were quantised and gathered by the routing launch, the second GEMM's by the first GEMM's epilogue)
     const uint8_t* in_hi = stage == 0 ? q_hi : q2_hi;
     const uint8_t* in_lo = stage == 0 ? q_lo : q2_lo;
     CUtensorMap tm_w, tm_hi, tm_lo;
