@@ -22,11 +22,12 @@
 // Per-CTA timestamps at 256 sequences (o_proj, 6 slices): accumulators complete at 7.7 us, dumped 9.3, cluster barrier
 // 10.1, reduction + epilogue done 20.0, exit 22.2.  The epilogue loop is what grows with the batch: a thread does
 // bn / (8 * slices) items one after the other and each item's loads (bias, residual, tables) must return before its
-// stores can issue, so an item costs one memory round trip - about 1.6 us with cold operands as the single-kernel
-// timing has them, less inside the model where the residual is in L2.  Two variants were measured and dropped: reading
-// the other slices' sums four at a time (23.5 against 23.8 us), and pushing every slice's sums into the shared memory
-// of the CTA that finishes the sequence so that the reduction reads locally (24.2 us: the remote reads were not the
-// cost).  What is left to do is to fetch the operands of several items before the first store.
+// stores can issue, and it adds the slices one distributed-shared-memory round trip after the other: about 1.6 us per
+// item with cold operands as the single-kernel timing has them.  All six warps now share the items (23.8 -> 21.3 us).
+// Variants measured and dropped, each removing one of the two chains only: the other slices' sums read four at a time
+// (23.5 us); every slice's sums pushed into the shared memory of the CTA that finishes the sequence, local reads
+// (24.2 us); three items' operands fetched before the first store (24.2 us); the last two together, with a remote store
+// and its address arithmetic per element (30.5 us).
 #include <cooperative_groups.h>
 
 #include <map>
@@ -117,7 +118,10 @@ __device__ __forceinline__ void st_bf16x4(__nv_bfloat16* p, bool vec, int n, con
 
 // TPC = weight tiles per CTA: 1, or 2 for the unembedding with many sequences (a compile-time constant so that the
 // common instantiation keeps straight-line producer / MMA code).
-template <int TPC>
+// LG: the unembedding's epilogue (logits / arg-max) instead of the projections' (cluster reduction, bias, RoPE, KV write,
+// residual): a compile-time choice so that neither epilogue's registers count against the other (the unembedding runs two
+// CTAs per SM and must stay under 170 registers; it needs 84 on its own).
+template <int TPC, bool LG>
 __global__ void __launch_bounds__(SK_THREADS, 1)
 skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const SkinnyArgs a,
                  int b0) {
@@ -234,7 +238,7 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = 0.f;
       }
-      if (a.epi == EPI_LOGITS) {
+      if (LG) {
 #pragma unroll
         for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(drow + c + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
       } else {  // sequence-major: the lanes of a warp (consecutive rows) write consecutive words
@@ -258,7 +262,8 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   tc_fence_before_sync();
   cluster.sync();  // every slice of the tile is in its CTA's shared memory
 
-  if (warp >= 2 && a.epi == EPI_LOGITS) {
+  if (LG) {
+   if (warp >= 2) {
     // ================================ unembedding: logits and per-tile arg-max (one K slice per tile) ================================
     const int e = (warp - 2) * 32 + lane;  // 0..127
     for (int h = 0; h < TPC; ++h) {
@@ -292,7 +297,8 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         }
       }
     }
-  } else if (a.epi != EPI_LOGITS && !*abort_flag) {
+   }
+  } else if (!*abort_flag) {
     // ================================ reduce across the cluster + epilogue ================================
     const int e = tid;  // all six warps: the producer and the MMA warp have nothing left to do
     long long offset = 0, pos = 0;
@@ -441,7 +447,7 @@ static int choose_kslices(int n_tiles, int nkb, int bn) {
   if (start > nkb) start = nkb;
   for (int ks = start; ks >= 1; --ks) {
     const size_t smem = skinny_smem_bytes(bn, nkb, ks, nullptr);
-    if (cudaFuncSetAttribute(skinny_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
+    if (cudaFuncSetAttribute(skinny_tc_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
         cudaSuccess) {
       (void)cudaGetLastError();
       continue;
@@ -458,7 +464,7 @@ static int choose_kslices(int n_tiles, int nkb, int bn) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int n_clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&n_clusters, skinny_tc_kernel<1>, &cfg) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveClusters(&n_clusters, skinny_tc_kernel<1, false>, &cfg) != cudaSuccess) {
       (void)cudaGetLastError();
       continue;
     }
@@ -520,10 +526,9 @@ static int launch_skinny(const void* x, int64_t x_stride, const void* w, SkinnyA
       if (a.bn > 128 && tunable(TUNE_UNEMBED_TILES) != 1) a.tpc = 2;
     }
     const size_t smem = skinny_smem_bytes(a.bn, a.nkb, ks, &a.stages, max_stages, a.tpc);
-    cudaError_t e = a.tpc == 2 ? cudaFuncSetAttribute(skinny_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                      static_cast<int>(smem))
-                               : cudaFuncSetAttribute(skinny_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                      static_cast<int>(smem));
+    auto kern = a.epi != EPI_LOGITS ? skinny_tc_kernel<1, false>
+                                    : (a.tpc == 2 ? skinny_tc_kernel<2, true> : skinny_tc_kernel<1, true>);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((a.n_tiles + a.tpc - 1) / a.tpc, ks, 1);
@@ -539,8 +544,7 @@ static int launch_skinny(const void* x, int64_t x_stride, const void* w, SkinnyA
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = tunable(TUNE_LAUNCH_OVERLAP) ? 2 : 1;
-    e = a.tpc == 2 ? cudaLaunchKernelEx(&cfg, skinny_tc_kernel<2>, tm_w, tm_x, a, b0)
-                   : cudaLaunchKernelEx(&cfg, skinny_tc_kernel<1>, tm_w, tm_x, a, b0);
+    e = cudaLaunchKernelEx(&cfg, kern, tm_w, tm_x, a, b0);
     if (e != cudaSuccess) {
       (void)cudaGetLastError();
       return static_cast<int>(e);
