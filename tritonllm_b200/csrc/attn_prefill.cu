@@ -54,6 +54,7 @@ constexpr int AP_BM = 128;       // query rows per unit
 constexpr int AP_BN = 64;        // keys per block
 constexpr int AP_D = 64;
 constexpr int AP_THREADS = 192;
+constexpr int AP_DEFAULT_POLY = 0;   // pairs of exponentials per pair computed on the FMA pipe (0: none); tunable "attn_prefill_poly"
 constexpr int AP_STAGES = 5;     // K+V blocks in flight per CTA (S = Q K^T runs three blocks ahead of O += P V)
 constexpr int AP_NSP = 3;        // S / P buffers in tensor memory
 constexpr int AP_Q_BYTES = AP_BM * AP_D * 2;     // 16 KiB
@@ -160,7 +161,11 @@ __device__ __forceinline__ int ap_unit_index(int i) {
 // exponential per score (config 3 full causal: 285.7 against 271.4 us; parity still green): the pack and unpack
 // conversions cost more issue slots than the exponential unit gives back, i.e. the softmax warps are bound by
 // instruction issue and dependency latency, not by that unit.  Kept as the record of the experiment.
-template <bool EXP16>
+// POLY (tunable "attn_prefill_poly", off): on blocks without masked scores, one pair of exponentials in every POLY pairs
+// is computed on the FMA pipe (ex2_poly) instead of the special-function unit, which two CTAs' softmax warps share.
+// Measured slower (config 3 full causal: 259 us without, 277 us with every 4th pair, 299 us with every 2nd; parity
+// green): like the fp16-pair experiment it says the softmax warps are not waiting for the special-function unit.
+template <bool EXP16, int POLY>
 __global__ void __launch_bounds__(AP_THREADS, 2)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const AttnPrefillArgs a) {
@@ -488,8 +493,13 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 p0 = f16lo_to_f32(ph);
                 p1 = f16hi_to_f32(ph);
               } else {
-                p0 = ex2_approx(fmaf(sv[c + e], scale_log2, neg_m));
-                p1 = ex2_approx(fmaf(sv[c + e + 1], scale_log2, neg_m));
+                if (POLY > 0 && ((e >> 1) % (POLY > 0 ? POLY : 1)) == (POLY > 0 ? POLY : 1) - 1) {
+                  p0 = ex2_poly(fmaf(sv[c + e], scale_log2, neg_m));
+                  p1 = ex2_poly(fmaf(sv[c + e + 1], scale_log2, neg_m));
+                } else {
+                  p0 = ex2_approx(fmaf(sv[c + e], scale_log2, neg_m));
+                  p1 = ex2_approx(fmaf(sv[c + e + 1], scale_log2, neg_m));
+                }
               }
               sum0 += p0;
               sum1 += p1;
@@ -648,11 +658,11 @@ B2_API int b2_attn_prefill(const void* q, const void* k, const void* v, const vo
   a.n_units = static_cast<int>(units);
 
   const size_t smem = sizeof(AttnPrefillSmem);
-  const bool exp32 = tunable(TUNE_ATTN_PREFILL_EXP16) == 0;
-  cudaError_t e = exp32 ? cudaFuncSetAttribute(attn_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               static_cast<int>(smem))
-                        : cudaFuncSetAttribute(attn_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               static_cast<int>(smem));
+  const bool exp16 = tunable(TUNE_ATTN_PREFILL_EXP16) != 0;
+  const int poly = tunable(TUNE_ATTN_PREFILL_POLY) < 0 ? 0 : (tunable(TUNE_ATTN_PREFILL_POLY) == 0 ? AP_DEFAULT_POLY : tunable(TUNE_ATTN_PREFILL_POLY));
+  auto kernel = exp16 ? attn_prefill_kernel<true, 0>
+                      : (poly == 2 ? attn_prefill_kernel<false, 2> : (poly == 4 ? attn_prefill_kernel<false, 4> : attn_prefill_kernel<false, 0>));
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return static_cast<int>(e);
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess ||
@@ -664,9 +674,6 @@ B2_API int b2_attn_prefill(const void* q, const void* k, const void* v, const vo
     long long* tb = trace_buffer(&slots);
     a.trace = slots >= static_cast<size_t>(grid) ? tb : nullptr;
   }
-  if (exp32)
-    attn_prefill_kernel<false><<<grid, AP_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(tm_q, tm_k, tm_v, a);
-  else
-    attn_prefill_kernel<true><<<grid, AP_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(tm_q, tm_k, tm_v, a);
+  kernel<<<grid, AP_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(tm_q, tm_k, tm_v, a);
   return launch_status();
 }

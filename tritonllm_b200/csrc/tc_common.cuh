@@ -230,6 +230,19 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+// 2^x on the FMA pipe instead of the special-function unit (x <= 127): x is rounded to the nearest integer n with the
+// 1.5 * 2^23 trick (n sits in the low mantissa bits of t), a cubic fitted to 2^r on [-0.5, 0.5] (max relative error
+// 7.5e-5, far below a bf16 rounding step) gives the fraction, and n is added to the exponent field as an integer.
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -126.f);
+  const float t = x + 12582912.f;
+  const float r = x - (t - 12582912.f);
+  float p = fmaf(0.05517167f, r, 0.24261113f);
+  p = fmaf(p, r, 0.69326097f);
+  p = fmaf(p, r, 0.99992806f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
 // Two exponentials per special-function instruction: the arguments as an fp16 pair (11 significant bits: an
 // argument below 16 in magnitude is off by at most 2^-8, i.e. 0.3 % of a result that is itself below 2^-8 of the
 // row maximum whenever the argument is that large), the results as an fp16 pair.
