@@ -58,7 +58,8 @@ def test_moe_golden(fp4):
 
 
 @pytest.mark.parametrize("T,E,H,I", [(1, 32, 2880, 2880), (5, 32, 2880, 2880), (32, 32, 2880, 2880),
-                                     (256, 32, 2880, 2880), (70, 128, 2880, 2880), (33, 8, 192, 320)])
+                                     (256, 32, 2880, 2880), (70, 128, 2880, 2880), (33, 8, 192, 320),
+                                     (40, 8, 256, 512)])   # the last: four k-blocks, so the last GEMM runs as two halves of two
 @pytest.mark.parametrize("fp4", FP4)
 def test_moe_vs_oracle(T, E, H, I, fp4):
     gen = torch.Generator().manual_seed(4000 + T + E)

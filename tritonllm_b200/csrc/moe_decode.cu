@@ -962,7 +962,9 @@ moe_expert_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
 // are still running in the last round stream faster when the others have finished, and the hand-off is not free.
 // =====================================================================================================
 constexpr int FPP_BN = 32;            // tokens of an expert per unit
-constexpr int FPP_STAGE_BYTES = FP4_A_BYTES + 2 * FPP_BN * 128 + 512 + 512;
+constexpr int FPP_BN_SMALL = 8;       // ... when the batch is so small that an expert gets a handful of tokens: the token
+                                      // tiles of a stage shrink from 8 KiB to 2 KiB and an SM holds ten stages instead of eight
+__host__ __device__ constexpr int fpp_stage_bytes(int bn) { return FP4_A_BYTES + 2 * bn * 128 + 512 + 512; }
 constexpr int FPP_DUMP_BYTES = 4096;
 constexpr int FPP_AHEAD = 4;          // k-blocks the token scale words are fetched ahead
 
@@ -996,12 +998,12 @@ __device__ __forceinline__ FppUnit fpp_unit(const MoeFp4Args& a, int i, int n_un
   u.kb1 = (u.kh + 1) * a.nkb / a.ksplit;
   u.e = a.meta->item_expert[item];
   const int part = a.meta->item_part[item];
-  u.n_e = min(a.meta->counts[u.e] - FPP_BN * part, FPP_BN);
-  u.row0 = a.meta->offsets[u.e] + FPP_BN * part;
+  u.n_e = min(a.meta->counts[u.e] - a.tok * part, a.tok);
+  u.row0 = a.meta->offsets[u.e] + a.tok * part;
   return u;
 }
 
-template <int EPI>
+template <int EPI, int BN>
 __global__ void __launch_bounds__(FP4_THREADS)
 moe_expert_fp4_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_hi,
                               const __grid_constant__ CUtensorMap tm_lo, const MoeFp4Args a) {
@@ -1014,7 +1016,7 @@ moe_expert_fp4_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __
   const int S = a.stages;
   uint8_t* atile = smem_raw;                                              // S x 16 KiB
   uint8_t* btile = atile + static_cast<size_t>(S) * FP4_A_BYTES;          // S x (32 hi rows, 32 lo rows) x 128
-  uint8_t* sfa_s = btile + static_cast<size_t>(S) * (2 * FPP_BN * 128);   // S x 512
+  uint8_t* sfa_s = btile + static_cast<size_t>(S) * (2 * BN * 128);   // S x 512
   uint8_t* sfb_s = sfa_s + static_cast<size_t>(S) * 512;                  // S x 512
   uint8_t* dump_s = sfb_s + static_cast<size_t>(S) * 512;                 // 4 KiB
   MoeFppBarriers& bar = *reinterpret_cast<MoeFppBarriers*>(dump_s + FPP_DUMP_BYTES);
@@ -1041,7 +1043,7 @@ moe_expert_fp4_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __
   // rows 64..127 of a token scale block are never written again: a harmless scale of 1
   for (int i = tid; i < S * 128; i += FP4_THREADS) reinterpret_cast<uint32_t*>(sfb_s)[i] = 0x7f7f7f7fu;
   fence_proxy_async_smem();
-  constexpr int TMEM_COLS = 128;   // accumulator 64, weight scales 4, token scales 4
+  constexpr int TMEM_COLS = BN == 32 ? 128 : 32;   // accumulator 2 * BN, weight scales 4, token scales 4
   if (warp == 1) tmem_alloc(&bar.tmem_base, TMEM_COLS);
   tc_fence_before_sync();
   __syncthreads();
@@ -1066,9 +1068,9 @@ moe_expert_fp4_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __
     };
     // row n2 of the [hi rows; lo rows] token tile: the four scale bytes of one k-block are one word
     auto load_tsf = [&](const Cur& c, int n2) -> uint32_t {
-      const int term = n2 >= FPP_BN, n = n2 - term * FPP_BN;
+      const int term = n2 >= BN, n = n2 - term * BN;
       const uint8_t* sf = term ? a.sf_lo : a.sf_hi;
-      return (c.u.valid && n < c.u.n_e)
+      return (c.u.valid && n2 < 2 * BN && n < c.u.n_e)
                  ? __ldg(reinterpret_cast<const uint32_t*>(sf + static_cast<size_t>(c.u.row0 + n) * sf_stride) + c.kb)
                  : 0x7f7f7f7fu;
     };
@@ -1098,18 +1100,18 @@ moe_expert_fp4_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __
       if (round > 0) ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar.empty[s], (round - 1) & 1, abort_flag));
       if (!ok) break;
       if (leader) {
-        mbar_arrive_expect_tx(&bar.full[s], static_cast<uint32_t>(FP4_A_TX + 512 + 2 * FPP_BN * 128));
+        mbar_arrive_expect_tx(&bar.full[s], static_cast<uint32_t>(FP4_A_TX + 512 + 2 * BN * 128));
         tma_load_4d(atile + static_cast<size_t>(s) * FP4_A_BYTES, &tm_w, &bar.full[s], cur.kb * FP4_KB, cur.u.tile * MOE_FT,
                     cur.u.e, 0);
         bulk_load(sfa_s + s * 512,
                   a.sfa + ((static_cast<size_t>(cur.u.e) * a.tiles + cur.u.tile) * nkb + cur.kb) * 512, 512, &bar.full[s]);
-        uint8_t* bt = btile + static_cast<size_t>(s) * (2 * FPP_BN * 128);
+        uint8_t* bt = btile + static_cast<size_t>(s) * (2 * BN * 128);
         tma_load_2d(bt, &tm_hi, &bar.full[s], cur.kb * FP4_KB, cur.u.row0);
-        tma_load_2d(bt + FPP_BN * 128, &tm_lo, &bar.full[s], cur.kb * FP4_KB, cur.u.row0);   // lo rows follow hi rows
+        tma_load_2d(bt + BN * 128, &tm_lo, &bar.full[s], cur.kb * FP4_KB, cur.u.row0);   // lo rows follow hi rows
       }
       uint8_t* blk = sfb_s + s * 512;
-      *reinterpret_cast<uint32_t*>(blk + off) = w0;
-      *reinterpret_cast<uint32_t*>(blk + off + 4) = w1;
+      if (lane < 2 * BN) *reinterpret_cast<uint32_t*>(blk + off) = w0;
+      if (BN == 32) *reinterpret_cast<uint32_t*>(blk + off + 4) = w1;
       fence_proxy_async_smem();   // tcgen05.cp reads the block through the async proxy
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar.full[s]);
@@ -1122,7 +1124,7 @@ moe_expert_fp4_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __
   } else if (warp == 1) {
     // ===================================== MMA issuer =====================================
     const bool leader = elect_one();
-    const uint32_t t_sfa = tmem + 2 * FPP_BN, t_sfb = t_sfa + 4;
+    const uint32_t t_sfa = tmem + 2 * BN, t_sfb = t_sfa + 4;
     bool ok = true;
     int g = 0;
     for (int i = 0; ok; ++i) {
@@ -1136,13 +1138,13 @@ moe_expert_fp4_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __
         if (!ok) break;
         tc_fence_after_sync();
         const uint64_t da = umma_desc_k128(smem_u32(atile + static_cast<size_t>(s) * FP4_A_BYTES));
-        const uint64_t db = umma_desc_k128(smem_u32(btile + static_cast<size_t>(s) * (2 * FPP_BN * 128)));
+        const uint64_t db = umma_desc_k128(smem_u32(btile + static_cast<size_t>(s) * (2 * BN * 128)));
         if (leader) {
           tmem_cp_sf_block(t_sfa, umma_desc_sf_block(smem_u32(sfa_s + s * 512)));
           tmem_cp_sf_block(t_sfb, umma_desc_sf_block(smem_u32(sfb_s + s * 512)));
 #pragma unroll
           for (int k = 0; k < FP4_KB / 32; ++k)
-            umma_fp4_fp8(tmem, da + 2 * k, db + 2 * k, umma_idesc_fp4_fp8(MOE_FT, 2 * FPP_BN, k, k), t_sfa, t_sfb,
+            umma_fp4_fp8(tmem, da + 2 * k, db + 2 * k, umma_idesc_fp4_fp8(MOE_FT, 2 * BN, k, k), t_sfa, t_sfb,
                          ((kb - u.kb0) | k) != 0);
           umma_commit(&bar.empty[s]);
           if (kb == u.kb1 - 1) umma_commit(&bar.acc_full);
@@ -1177,14 +1179,19 @@ moe_expert_fp4_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __
         break;
       }
       tc_fence_after_sync();
-      float v[32];
-      {   // columns 0..31 hold the hi term's sums, columns 32..63 the lo term's
+      float v[32];   // tokens 0 .. BN-1 are meaningful
+      if constexpr (BN == 32) {   // columns 0..31 hold the hi term's sums, columns 32..63 the lo term's
         float w[32];
         tmem_ld_32x32_nowait(trow, v);
-        tmem_ld_32x32_nowait(trow + FPP_BN, w);
+        tmem_ld_32x32_nowait(trow + BN, w);
         tmem_wait_ld();
 #pragma unroll
         for (int t = 0; t < 32; ++t) v[t] += w[t];
+      } else {                    // one load covers the allocation: hi sums in columns 0..BN-1, lo sums in BN..2BN-1
+        float w[32];
+        tmem_ld_32x32(trow, w);
+#pragma unroll
+        for (int t = 0; t < 32; ++t) v[t] = t < BN ? w[t] + w[(t + BN) & 31] : 0.f;
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -1192,7 +1199,7 @@ moe_expert_fp4_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __
 
       if constexpr (EPI == MOE_EPI_SWIGLU) {
 #pragma unroll
-        for (int t = 0; t < 32; ++t) {
+        for (int t = 0; t < BN; ++t) {
           const float xv = v[t] + bias;
           const float other = __shfl_xor_sync(0xffffffffu, xv, 1);
           if ((lane & 1) == 0) dump[t * OUT_F + (fr >> 1)] = __float2bfloat16_rn(moe_swiglu(xv, other, a.alpha, a.limit));
@@ -1236,22 +1243,23 @@ moe_expert_fp4_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");   // the dump is free for the next unit
       } else {
-        // 128 features x 16 tokens fill the 4 KiB: two passes
+        // 128 features x 16 tokens fill the 4 KiB: two passes for 32 tokens
+        constexpr int PASS = BN < 16 ? BN : 16;
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
+        for (int half = 0; half < BN / PASS; ++half) {
 #pragma unroll
-          for (int t = 0; t < 16; ++t) {
-            const int tok = 16 * half + t;
+          for (int t = 0; t < PASS; ++t) {
+            const int tok = PASS * half + t;
             const float gw = tok < u.n_e ? a.meta->gate_of_row[u.row0 + tok] : 0.f;
             dump[t * OUT_F + fr] = __float2bfloat16_rn((v[tok] + bias) * gw);
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");
-          const int n_here = min(u.n_e - 16 * half, 16);
+          const int n_here = min(u.n_e - PASS * half, PASS);
           for (int it = t4; it < n_here * PIECES; it += 128) {
             const int tok = it / PIECES, pc = it - tok * PIECES;
             const int col = u.tile * OUT_F + pc * 8;
             if (col + 8 <= out_n)
-              *reinterpret_cast<uint4*>(a.out + u.kh * a.out_half_stride + static_cast<size_t>(u.row0 + 16 * half + tok) * out_n + col) =
+              *reinterpret_cast<uint4*>(a.out + u.kh * a.out_half_stride + static_cast<size_t>(u.row0 + PASS * half + tok) * out_n + col) =
                   *reinterpret_cast<const uint4*>(dump + tok * OUT_F + pc * 8);
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -1453,6 +1461,7 @@ moe_combine_add_norm_kernel(const __nv_bfloat16* __restrict__ y, const MoeMeta* 
 
 // ------------------------------------------------------------------------------- FP4 tensor-core path
 namespace {
+bool T_small(int64_t tokens, int n_experts) { return tokens <= n_experts && tokens <= 128; }
 // How b2_moe_experts_decode_fp4 runs under the current tuning knobs; b2_moe_combine_add_rmsnorm must agree with it on
 // where the last GEMM's second partial rows are.
 struct MoeFp4Plan {
@@ -1534,7 +1543,13 @@ B2_API int b2_moe_experts_decode_fp4(const void* x, int64_t ldx, const int16_t* 
   const int bn_all = ((T < MOE_MAX_TOKENS ? T : MOE_MAX_TOKENS) + 31) & ~31;
   // 32 tokens of an expert per CTA: two stages, four CTAs per SM.  With the item list this beats 64 tokens (three
   // stages, two CTAs per SM) at every size measured (256 tokens: 166 against 183 us; 2048: 769 against 786 us)
-  const MoeFp4Plan plan = moe_fp4_plan(tokens, intermediate);
+  MoeFp4Plan plan = moe_fp4_plan(tokens, intermediate);
+  // a handful of tokens per expert (at most one per expert on average): 8-token parts, 2 CTAs x 5 stages per SM
+  const bool small_parts = plan.per_sm > 0 && tunable(TUNE_MOE_FP4_TOK) != 32 && T_small(tokens, n_experts);
+  if (small_parts) {
+    plan.tok = FPP_BN_SMALL;
+    plan.per_sm = 2;
+  }
   const int tok = plan.tok;
   // the first GEMM's input rows are dead when the last GEMM runs: its second partial rows go there
   __nv_bfloat16* ybuf2 = reinterpret_cast<__nv_bfloat16*>(q_hi);
@@ -1576,7 +1591,7 @@ B2_API int b2_moe_experts_decode_fp4(const void* x, int64_t ldx, const int16_t* 
     if (rc != B2_OK) return rc;
     const uint64_t xd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(rows)};
     const uint64_t xstr[1] = {static_cast<uint64_t>(K)};
-    const uint32_t xbox[2] = {FP4_KB, 32};
+    const uint32_t xbox[2] = {FP4_KB, small_parts ? static_cast<uint32_t>(FPP_BN_SMALL) : 32u};
     rc = make_tensor_map(&tm_hi, CU_TENSOR_MAP_DATA_TYPE_UINT8, in_hi, 2, xd, xstr, xbox, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != B2_OK) return rc;
     rc = make_tensor_map(&tm_lo, CU_TENSOR_MAP_DATA_TYPE_UINT8, in_lo, 2, xd, xstr, xbox, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -1612,25 +1627,21 @@ B2_API int b2_moe_experts_decode_fp4(const void* x, int64_t ldx, const int16_t* 
     if (plan.per_sm > 0) {
       // persistent CTAs over the (expert part, weight tile) list: `per_sm` CTAs per SM share the 8 stages an SM has room for
       const int per_sm = plan.per_sm;
-      a.stages = FP4_MAX_STAGES / per_sm;
+      a.stages = small_parts ? 5 : FP4_MAX_STAGES / per_sm;
       if (tunable(TUNE_MOE_FP4_STAGES) >= 2 && tunable(TUNE_MOE_FP4_STAGES) <= a.stages) a.stages = tunable(TUNE_MOE_FP4_STAGES);
-      const size_t psmem = static_cast<size_t>(a.stages) * FPP_STAGE_BYTES + FPP_DUMP_BYTES + sizeof(MoeFppBarriers);
+      const size_t psmem = static_cast<size_t>(a.stages) * fpp_stage_bytes(tok) + FPP_DUMP_BYTES + sizeof(MoeFppBarriers);
       int dev = 0, sms = 0;
       cudaGetDevice(&dev);
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
       const long long max_units = static_cast<long long>(a.tiles) * a.ksplit * (rows / tok + n_experts);
       const unsigned pgrid = static_cast<unsigned>(std::min<long long>(static_cast<long long>(per_sm) * sms, max_units));
-      if (stage == 0) {
-        e = cudaFuncSetAttribute(moe_expert_fp4_persist_kernel<MOE_EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(psmem));
-        if (e != cudaSuccess) return static_cast<int>(e);
-        launch_overlapped(moe_expert_fp4_persist_kernel<MOE_EPI_SWIGLU>, dim3(pgrid), dim3(FP4_THREADS), psmem, st, tm_w, tm_hi, tm_lo, a);
-      } else {
-        e = cudaFuncSetAttribute(moe_expert_fp4_persist_kernel<MOE_EPI_GATE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(psmem));
-        if (e != cudaSuccess) return static_cast<int>(e);
-        launch_overlapped(moe_expert_fp4_persist_kernel<MOE_EPI_GATE>, dim3(pgrid), dim3(FP4_THREADS), psmem, st, tm_w, tm_hi, tm_lo, a);
-      }
+      auto kern = stage == 0 ? (small_parts ? moe_expert_fp4_persist_kernel<MOE_EPI_SWIGLU, FPP_BN_SMALL>
+                                            : moe_expert_fp4_persist_kernel<MOE_EPI_SWIGLU, FPP_BN>)
+                             : (small_parts ? moe_expert_fp4_persist_kernel<MOE_EPI_GATE, FPP_BN_SMALL>
+                                            : moe_expert_fp4_persist_kernel<MOE_EPI_GATE, FPP_BN>);
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(psmem));
+      if (e != cudaSuccess) return static_cast<int>(e);
+      launch_overlapped(kern, dim3(pgrid), dim3(FP4_THREADS), psmem, st, tm_w, tm_hi, tm_lo, a);
     } else if (stage == 0) {
       e = cudaFuncSetAttribute(moe_expert_fp4_kernel<MOE_EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(smem));
