@@ -27,7 +27,7 @@ static void init_tunables() {
     g_tunables[TUNE_ATTN_DECODE_STAGES] = 3;
     g_tunables[TUNE_GEMM_PAIR] = 1;  // 1: large GEMMs run on CTA pairs (cta_group::2); 2: pairs, one k-block per stage; 0: one CTA per tile
     g_tunables[TUNE_MOE_FP4_STAGES] = 0;  // 0: chosen from the token-tile size
-    g_tunables[TUNE_MOE_FP4_TOK] = 0;      // 32 / 64: tokens of an expert per CTA (0: 32)
+    g_tunables[TUNE_MOE_FP4_TOK] = 0;      // 8 / 16 / 32 / 64: tokens of an expert per CTA (0: by the batch size; 64: the one-shot kernel)
     g_tunables[TUNE_UNEMBED_STAGES] = 0;   // ring depth of the unembedding kernel (0: as deep as shared memory allows)
     g_tunables[TUNE_MOE_PREFETCH] = 0;     // k-blocks of expert weights requested into L2 ahead of the shared-memory ring (0: off; 3-12 measured no faster)
     g_tunables[TUNE_ATTN_PREFILL_EXP16] = 0;   // 1: prefill attention computes its exponentials two at a time on fp16 pairs (measured slower)

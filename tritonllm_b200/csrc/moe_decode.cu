@@ -1043,7 +1043,7 @@ moe_expert_fp4_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __
   // rows 64..127 of a token scale block are never written again: a harmless scale of 1
   for (int i = tid; i < S * 128; i += FP4_THREADS) reinterpret_cast<uint32_t*>(sfb_s)[i] = 0x7f7f7f7fu;
   fence_proxy_async_smem();
-  constexpr int TMEM_COLS = BN == 32 ? 128 : 32;   // accumulator 2 * BN, weight scales 4, token scales 4
+  constexpr int TMEM_COLS = BN == 32 ? 128 : (BN == 16 ? 64 : 32);   // accumulator 2 * BN, weight scales 4, token scales 4
   if (warp == 1) tmem_alloc(&bar.tmem_base, TMEM_COLS);
   tc_fence_before_sync();
   __syncthreads();
@@ -1461,7 +1461,13 @@ moe_combine_add_norm_kernel(const __nv_bfloat16* __restrict__ y, const MoeMeta* 
 
 // ------------------------------------------------------------------------------- FP4 tensor-core path
 namespace {
-bool T_small(int64_t tokens, int n_experts) { return tokens <= n_experts && tokens <= 128; }
+// Tokens of an expert per unit of the persistent kernel, by the average number of routed rows per expert (4 * tokens /
+// experts): up to 4 -> 8, up to 8 -> 16, else 32 (measured, whole op at 32 / 64 / 128 tokens and 32 experts: 8-token
+// parts 96 / 123 / 204 us, 16-token parts 100 / 101 / 128 us, 32-token parts 104 / 108 / 112 us).
+int moe_part_tokens(int64_t tokens, int n_experts) {
+  if (tokens > 128) return 32;
+  return tokens <= n_experts ? 8 : (tokens <= 2 * n_experts ? 16 : 32);
+}
 // How b2_moe_experts_decode_fp4 runs under the current tuning knobs; b2_moe_combine_add_rmsnorm must agree with it on
 // where the last GEMM's second partial rows are.
 struct MoeFp4Plan {
@@ -1544,10 +1550,12 @@ B2_API int b2_moe_experts_decode_fp4(const void* x, int64_t ldx, const int16_t* 
   // 32 tokens of an expert per CTA: two stages, four CTAs per SM.  With the item list this beats 64 tokens (three
   // stages, two CTAs per SM) at every size measured (256 tokens: 166 against 183 us; 2048: 769 against 786 us)
   MoeFp4Plan plan = moe_fp4_plan(tokens, intermediate);
-  // a handful of tokens per expert (at most one per expert on average): 8-token parts, 2 CTAs x 5 stages per SM
-  const bool small_parts = plan.per_sm > 0 && tunable(TUNE_MOE_FP4_TOK) != 32 && T_small(tokens, n_experts);
+  // a handful of tokens per expert: 8- or 16-token parts, 2 CTAs x 5 stages per SM (tunable moe_fp4_tok = 8 / 16 / 32 forces one)
+  int part = tunable(TUNE_MOE_FP4_TOK) == 0 ? moe_part_tokens(tokens, n_experts) : tunable(TUNE_MOE_FP4_TOK);
+  if (tokens > 128 && part < 32) part = 32;   // the item list is sized for 32-token parts beyond that
+  const bool small_parts = plan.per_sm > 0 && (part == 8 || part == 16);
   if (small_parts) {
-    plan.tok = FPP_BN_SMALL;
+    plan.tok = part;
     plan.per_sm = 2;
   }
   const int tok = plan.tok;
@@ -1591,7 +1599,7 @@ B2_API int b2_moe_experts_decode_fp4(const void* x, int64_t ldx, const int16_t* 
     if (rc != B2_OK) return rc;
     const uint64_t xd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(rows)};
     const uint64_t xstr[1] = {static_cast<uint64_t>(K)};
-    const uint32_t xbox[2] = {FP4_KB, small_parts ? static_cast<uint32_t>(FPP_BN_SMALL) : 32u};
+    const uint32_t xbox[2] = {FP4_KB, small_parts ? static_cast<uint32_t>(tok) : 32u};
     rc = make_tensor_map(&tm_hi, CU_TENSOR_MAP_DATA_TYPE_UINT8, in_hi, 2, xd, xstr, xbox, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != B2_OK) return rc;
     rc = make_tensor_map(&tm_lo, CU_TENSOR_MAP_DATA_TYPE_UINT8, in_lo, 2, xd, xstr, xbox, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -1635,9 +1643,11 @@ B2_API int b2_moe_experts_decode_fp4(const void* x, int64_t ldx, const int16_t* 
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
       const long long max_units = static_cast<long long>(a.tiles) * a.ksplit * (rows / tok + n_experts);
       const unsigned pgrid = static_cast<unsigned>(std::min<long long>(static_cast<long long>(per_sm) * sms, max_units));
-      auto kern = stage == 0 ? (small_parts ? moe_expert_fp4_persist_kernel<MOE_EPI_SWIGLU, FPP_BN_SMALL>
+      auto kern = stage == 0 ? (tok == 8    ? moe_expert_fp4_persist_kernel<MOE_EPI_SWIGLU, 8>
+                                : tok == 16 ? moe_expert_fp4_persist_kernel<MOE_EPI_SWIGLU, 16>
                                             : moe_expert_fp4_persist_kernel<MOE_EPI_SWIGLU, FPP_BN>)
-                             : (small_parts ? moe_expert_fp4_persist_kernel<MOE_EPI_GATE, FPP_BN_SMALL>
+                             : (tok == 8    ? moe_expert_fp4_persist_kernel<MOE_EPI_GATE, 8>
+                                : tok == 16 ? moe_expert_fp4_persist_kernel<MOE_EPI_GATE, 16>
                                             : moe_expert_fp4_persist_kernel<MOE_EPI_GATE, FPP_BN>);
       e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(psmem));
       if (e != cudaSuccess) return static_cast<int>(e);
