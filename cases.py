@@ -315,7 +315,6 @@ def generate_case(a):
     the step replayed from one CUDA graph.  Random weights of the 20b architecture (`--layers`, `--moe-experts`)."""
     from tritonllm_b200 import generate as G
     dev = "cuda"
-    ops.set_expanded_expert_budget(int(a.expanded_gb * (1 << 30)))
     B, P, N = a.batch, a.prompt, a.new_tokens
     cfg = G.ModelConfig(num_hidden_layers=a.layers, num_experts=a.moe_experts or 32)
     model = G.Transformer(cfg, G.ModelWeights.random(cfg, dev, seed=1239, fp4=not a.no_fp4), max_context=max(P + N, 4096))
@@ -380,7 +379,7 @@ def _parser():
                          "rmsnorm, rope, qkv_decode, oproj_decode); needs a TritonLLM checkout and triton")
     ap.add_argument("--tune", action="append", default=[], help="name=value tuning knob (b2_set_tunable)")
     ap.add_argument("--expanded-gb", type=float, default=0.0,
-                    help="generate: device memory (GB) that may hold resident bf16 copies of the expert weights for the prompt path")
+                    help="generate / moe_prefill: device memory (GB) that may hold resident bf16 copies of the expert weights for the prompt path")
     ap.add_argument("--phase-trace", action="store_true",
                     help="attn_prefill: also print the softmax warps' per-phase clock counters (diagnostic build of the library)")
     return ap
@@ -491,6 +490,7 @@ def main():
     for kv in a.tune:
         name, val = kv.split("=")
         _lib.check("b2_set_tunable", lib.b2_set_tunable(name.encode(), int(val)))
+    ops.set_expanded_expert_budget(int(a.expanded_gb * (1 << 30)))
     if a.case == "generate":
         return generate_case(a)
     if a.case == "decode_stack":
