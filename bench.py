@@ -632,7 +632,7 @@ def run_b200(args, rank: int, world: int, local_rank: int):
     }
     if not args.no_decode:
         ok = decode_err is None and dw < 1e29
-        dec = {"unit": "tokens/s", "error": decode_err, "gpu_launches_per_step": 24 * 8 + 4,
+        dec = {"unit": "tokens/s", "error": decode_err, "gpu_launches_per_step": 24 * 7 + 4,
                "workload": "config 5: gpt-oss-20b shape, whole model (24 layers, 32 experts top-4 MXFP4, vocab 201088), random "
                            f"weights, {DECODE_PROMPT}-token seeded random prompts really ingested, {DECODE_NEW} tokens generated greedily, "
                            "one CUDA graph replay per step, CUDA events, max over ranks",

@@ -73,6 +73,29 @@ def test_moe_vs_oracle(T, E, H, I, fp4):
     assert_parity(ref, out, f"moe T={T} E={E} fp4={fp4}")
 
 
+@pytest.mark.parametrize("knobs", [{"moe_fp4_fuse": 2, "moe_fp4_tok": 8}, {"moe_fp4_fuse": 2, "moe_fp4_tok": 16},
+                                   {"moe_fp4_fuse": 1, "moe_fp4_tok": 32}, {"moe_fp4_fuse": 1, "moe_fp4_ksplit": 1},
+                                   {"moe_fp4_persist": 0}, {"moe_fp4_persist": 2}])
+def test_moe_fp4_kernel_variants_agree_with_the_oracle(knobs):
+    """The FP4 path picks its kernel by batch size (part size, one fused launch or two, half-k units, persistent or
+    one-shot); every variant is forced here on the same 72-token batch."""
+    from tritonllm_b200 import _lib
+    lib = _lib.load()
+    T, E, H, I = 72, 32, 2880, 2880
+    gen = torch.Generator().manual_seed(4100)
+    x = torch.randn(T, H, generator=gen).bfloat16()
+    vals, idx, _ = O.topk_softmax(torch.randn(T, E, generator=gen), 4)
+    w1, w2 = _random_experts(gen, E, 2 * I, H), _random_experts(gen, E, H, I)
+    try:
+        for k, v in knobs.items():
+            _lib.check("b2_set_tunable", lib.b2_set_tunable(k.encode(), v))
+        out = _run(x, vals, idx, w1, w2, True)
+    finally:
+        for k in knobs:
+            _lib.check("b2_set_tunable", lib.b2_set_tunable(k.encode(), 0 if k != "moe_fp4_persist" else 4))
+    assert_parity(_oracle(x, vals, idx, w1, w2), out, f"moe fp4 variant {knobs}")
+
+
 @pytest.mark.parametrize("fp4", FP4)
 def test_moe_all_tokens_one_expert_set(fp4):
     """Every token picks the same four experts: 256 rows per expert, the largest token tile."""

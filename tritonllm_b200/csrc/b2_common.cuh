@@ -30,7 +30,7 @@ int sm_count();
 int tunable(int id);
 // Optional per-CTA timestamp buffer (8 x int64 per CTA) set with b2_set_trace_buffer; NULL when tracing is off.
 long long* trace_buffer(size_t* slots);
-enum Tunable { TUNE_ATTN_DECODE_CTAS_PER_SM = 0, TUNE_GEMV_KSPLIT_QKV, TUNE_GEMV_KSPLIT_OUT, TUNE_TMA_L2_PROMOTION, TUNE_ATTN_DECODE_STAGES, TUNE_GEMM_PAIR, TUNE_MOE_FP4_STAGES, TUNE_LAUNCH_OVERLAP, TUNE_MOE_FP4_TOK, TUNE_UNEMBED_STAGES, TUNE_MOE_PREFETCH, TUNE_ATTN_PREFILL_EXP16, TUNE_RMSNORM_WARPS, TUNE_RMSNORM_RING_MIN_ROWS, TUNE_UNEMBED_TILES, TUNE_MOE_FP4_PERSIST, TUNE_MOE_FP4_KSPLIT, TUNE_ATTN_PREFILL_POLY, TUNE_COUNT };
+enum Tunable { TUNE_ATTN_DECODE_CTAS_PER_SM = 0, TUNE_GEMV_KSPLIT_QKV, TUNE_GEMV_KSPLIT_OUT, TUNE_TMA_L2_PROMOTION, TUNE_ATTN_DECODE_STAGES, TUNE_GEMM_PAIR, TUNE_MOE_FP4_STAGES, TUNE_LAUNCH_OVERLAP, TUNE_MOE_FP4_TOK, TUNE_UNEMBED_STAGES, TUNE_MOE_PREFETCH, TUNE_ATTN_PREFILL_EXP16, TUNE_RMSNORM_WARPS, TUNE_RMSNORM_RING_MIN_ROWS, TUNE_UNEMBED_TILES, TUNE_MOE_FP4_PERSIST, TUNE_MOE_FP4_KSPLIT, TUNE_ATTN_PREFILL_POLY, TUNE_MOE_FP4_FUSE, TUNE_COUNT };
 
 // Encodes a tiled tensor map for a bf16 tensor of up to 5 dims (dim 0 innermost, stride 1).
 // strides_bytes[i] is the byte stride of dim i+1.  Returns a B2 status.

@@ -54,6 +54,7 @@ struct MoeMeta {          // lives at the start of the workspace
   int n_items;
   short item_expert[MOE_MAX_ITEMS];
   short item_part[MOE_MAX_ITEMS];
+  int item_done[MOE_MAX_ITEMS];   // fused expert kernel: weight tiles of the first GEMM finished per item (zeroed by the routing kernel)
 };
 
 // ------------------------------------------------------------------------------------------- routing
@@ -68,6 +69,7 @@ __device__ __forceinline__ void moe_route_body(const int16_t* __restrict__ topk_
   for (int i = tid; i < n_experts * words; i += blockDim.x) mask[i / words][i % words] = 0u;
   __syncthreads();
   overlap_wait();
+  for (int i = tid; i < MOE_MAX_ITEMS; i += blockDim.x) meta->item_done[i] = 0;
   const int slots = tokens * MOE_TOPK;
   for (int sl = tid; sl < slots; sl += blockDim.x) {
     const int t = sl / MOE_TOPK, e = topk_idx[sl];
@@ -980,12 +982,14 @@ struct __align__(16) MoeFppBarriers {
 struct FppUnit {   // one (expert part, weight tile[, half of the k range]) of the CTA's list
   int e, row0, n_e, tile;
   int kh, kb0, kb1;   // which part of the k range, and its k-blocks [kb0, kb1)
+  int side, item;     // fused kernel: which GEMM (0 / 1) and which (expert, part) of the item list
   bool valid;
 };
 __device__ __forceinline__ FppUnit fpp_unit(const MoeFp4Args& a, int i, int n_units) {
   FppUnit u;
   const int w = static_cast<int>(blockIdx.x) + i * static_cast<int>(gridDim.x);
   u.valid = w < n_units;
+  u.side = u.item = 0;
   if (!u.valid) {
     u.e = u.row0 = u.n_e = u.tile = u.kh = u.kb0 = u.kb1 = 0;
     return u;
@@ -1243,6 +1247,417 @@ moe_expert_fp4_persist_kernel(const __grid_constant__ CUtensorMap tm_w, const __
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");   // the dump is free for the next unit
       } else {
+        // 128 features x 16 tokens fill the 4 KiB: two passes for 32 tokens
+        constexpr int PASS = BN < 16 ? BN : 16;
+#pragma unroll
+        for (int half = 0; half < BN / PASS; ++half) {
+#pragma unroll
+          for (int t = 0; t < PASS; ++t) {
+            const int tok = PASS * half + t;
+            const float gw = tok < u.n_e ? a.meta->gate_of_row[u.row0 + tok] : 0.f;
+            dump[t * OUT_F + fr] = __float2bfloat16_rn((v[tok] + bias) * gw);
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          const int n_here = min(u.n_e - PASS * half, PASS);
+          for (int it = t4; it < n_here * PIECES; it += 128) {
+            const int tok = it / PIECES, pc = it - tok * PIECES;
+            const int col = u.tile * OUT_F + pc * 8;
+            if (col + 8 <= out_n)
+              *reinterpret_cast<uint4*>(a.out + u.kh * a.out_half_stride + static_cast<size_t>(u.row0 + PASS * half + tok) * out_n + col) =
+                  *reinterpret_cast<const uint4*>(dump + tok * OUT_F + pc * 8);
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+
+// =====================================================================================================
+// Both expert GEMMs in one persistent launch.  The unit list is the first GEMM's units followed by the second's; the
+// CTAs walk it with a stride of the grid as above, so the second GEMM's first units fill the SMs that the first GEMM's
+// last, partly empty round would leave idle, and there is no launch boundary between the two.  A unit of the second
+// GEMM depends on all weight tiles of the first GEMM for the same (expert, part): each of those counts itself in
+// MoeMeta::item_done after storing its rows (release), and the producer warp of the dependent unit waits (bounded,
+// acquire) before it requests anything the first GEMM wrote.  Every CTA of the grid is resident (the host sizes the grid
+// by registers, shared memory and tensor memory), and a unit only ever waits for units that come earlier in every
+// CTA's list, so the waits always end.
+// =====================================================================================================
+struct MoeFusedArgs {
+  const uint8_t* sfa[2];     // per GEMM: weight scale blocks, the input rows' scale bytes (hi, lo), bias
+  const uint8_t* sf_hi[2];
+  const uint8_t* sf_lo[2];
+  const float* bias[2];
+  int N[2], nkb[2], tiles[2];
+  int ksplit2;               // parts of the second GEMM's k range per weight tile (1 or 2)
+  const MoeMeta* meta;
+  int* item_done;            // MoeMeta::item_done (zeroed by the routing kernel)
+  __nv_bfloat16* out;        // second GEMM: rows [rows][N[1]]; the second half-k partial out_half_stride elements further
+  int64_t out_half_stride;
+  uint8_t* q2_hi;            // first GEMM's epilogue output = second GEMM's input
+  uint8_t* q2_lo;
+  uint8_t* sf2_hi;
+  uint8_t* sf2_lo;
+  int K2, sf2_stride;
+  int stages, tok;
+  float alpha, limit;
+  int* status;
+};
+
+__device__ __forceinline__ FppUnit fused_unit(const MoeFusedArgs& a, int i) {
+  FppUnit u;
+  const int w = static_cast<int>(blockIdx.x) + i * static_cast<int>(gridDim.x);
+  const int n_items = a.meta->n_items;
+  const int n1 = n_items * a.tiles[0];
+  u.valid = w < n1 + n_items * a.tiles[1] * a.ksplit2;
+  u.side = 0;
+  u.item = 0;
+  if (!u.valid) {
+    u.e = u.row0 = u.n_e = u.tile = u.kh = u.kb0 = u.kb1 = 0;
+    return u;
+  }
+  if (w < n1) {
+    u.item = w / a.tiles[0];
+    u.tile = w - u.item * a.tiles[0];
+    u.kh = 0;
+    u.kb0 = 0;
+    u.kb1 = a.nkb[0];
+  } else {
+    u.side = 1;
+    const int w2 = w - n1, per_item = a.tiles[1] * a.ksplit2;
+    u.item = w2 / per_item;
+    const int rem = w2 - u.item * per_item;
+    u.tile = rem / a.ksplit2;
+    u.kh = rem - u.tile * a.ksplit2;
+    u.kb0 = u.kh * a.nkb[1] / a.ksplit2;
+    u.kb1 = (u.kh + 1) * a.nkb[1] / a.ksplit2;
+  }
+  u.e = a.meta->item_expert[u.item];
+  const int part = a.meta->item_part[u.item];
+  u.n_e = min(a.meta->counts[u.e] - a.tok * part, a.tok);
+  u.row0 = a.meta->offsets[u.e] + a.tok * part;
+  return u;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(FP4_THREADS, 4)
+moe_expert_fp4_fused_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__ CUtensorMap tm_hi1,
+                            const __grid_constant__ CUtensorMap tm_lo1, const __grid_constant__ CUtensorMap tm_w2,
+                            const __grid_constant__ CUtensorMap tm_hi2, const __grid_constant__ CUtensorMap tm_lo2,
+                            const MoeFusedArgs a) {
+  overlap_start();
+  overlap_wait();
+  const int n_units = a.meta->n_items * (a.tiles[0] + a.tiles[1] * a.ksplit2);
+  if (static_cast<int>(blockIdx.x) >= n_units) return;
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const int S = a.stages;
+  uint8_t* atile = smem_raw;                                              // S x 16 KiB
+  uint8_t* btile = atile + static_cast<size_t>(S) * FP4_A_BYTES;          // S x (32 hi rows, 32 lo rows) x 128
+  uint8_t* sfa_s = btile + static_cast<size_t>(S) * (2 * BN * 128);   // S x 512
+  uint8_t* sfb_s = sfa_s + static_cast<size_t>(S) * 512;                  // S x 512
+  uint8_t* dump_s = sfb_s + static_cast<size_t>(S) * 512;                 // 4 KiB
+  MoeFppBarriers& bar = *reinterpret_cast<MoeFppBarriers*>(dump_s + FPP_DUMP_BYTES);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  volatile int* abort_flag = &bar.abort_flag;
+  if ((smem_u32(smem_raw) & 1023u) != 0) {   // the swizzled tiles need this alignment
+    if (tid == 0) atomicOr(a.status, B2_DEV_BAD_INDEX);
+    return;
+  }
+
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&bar.full[s], 2);
+      mbar_init(&bar.empty[s], 1);
+    }
+    mbar_init(&bar.acc_full, 1);
+    mbar_init(&bar.acc_empty, 4);
+    bar.abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_w1);
+    tma_prefetch_desc(&tm_hi1);
+    tma_prefetch_desc(&tm_lo1);
+    tma_prefetch_desc(&tm_w2);
+    tma_prefetch_desc(&tm_hi2);
+    tma_prefetch_desc(&tm_lo2);
+  }
+  // rows 64..127 of a token scale block are never written again: a harmless scale of 1
+  for (int i = tid; i < S * 128; i += FP4_THREADS) reinterpret_cast<uint32_t*>(sfb_s)[i] = 0x7f7f7f7fu;
+  fence_proxy_async_smem();
+  constexpr int TMEM_COLS = BN == 32 ? 128 : (BN == 16 ? 64 : 32);   // accumulator 2 * BN, weight scales 4, token scales 4
+  if (warp == 1) tmem_alloc(&bar.tmem_base, TMEM_COLS);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = bar.tmem_base;
+
+  if (warp == 0) {
+    // ===================================== producer + token scale blocks =====================================
+    const bool leader = elect_one();
+    bool ok = true;
+    // A unit of the second GEMM reads what the first GEMM's epilogues wrote for its (expert, part): every weight tile of
+    // the first GEMM counts itself in item_done when its rows are stored.  The cursor that runs ahead for the scale
+    // words only LOOKS at the count when it enters such a unit (the usual case: complete long ago) and remembers the
+    // answer; the blocking wait (bounded), if it is needed at all, is taken when the loading cursor itself reaches the
+    // unit - by then every load of this CTA's own earlier units, on whose epilogues the count may depend, has been
+    // issued, so the wait cannot keep this CTA's own contribution from happening.
+    auto wait_item = [&](const FppUnit& u, bool block) -> bool {
+      if (!u.valid || u.side == 0) return true;
+      int seen = 0;
+      if (lane == 0) {
+        const int* cnt = a.item_done + u.item;
+        uint64_t t0 = 0;
+        for (uint32_t spin = 0; spin < SPIN_LIMIT; ++spin) {
+          int v;
+          asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
+          if (v >= a.tiles[0]) {
+            seen = 1;
+            break;
+          }
+          if (!block) break;
+          if ((spin & 63u) == 63u) {
+            if (*abort_flag) break;
+            const uint64_t now = wait_clock_ns();
+            if (t0 == 0)
+              t0 = now;
+            else if (now - t0 > WAIT_LIMIT_NS)
+              break;
+          }
+        }
+      }
+      seen = __shfl_sync(0xffffffffu, seen, 0);
+      if (!seen && block) ok = false;
+      asm volatile("fence.proxy.async;" ::: "memory");   // the TMA loads that follow read other CTAs' generic stores
+      return seen != 0;
+    };
+    struct Cur {
+      int i, kb;
+      FppUnit u;
+    };
+    uint32_t ready_mask = 0;   // bit (unit iteration & 31): the look-ahead cursor found the unit's input complete
+    auto enter_ahead = [&](const Cur& c) {
+      const uint32_t bit = 1u << (c.i & 31);
+      ready_mask = wait_item(c.u, false) ? (ready_mask | bit) : (ready_mask & ~bit);
+    };
+    auto next = [&](Cur& c, bool ahead) {
+      if (++c.kb >= c.u.kb1) {
+        ++c.i;
+        c.u = fused_unit(a, c.i);
+        c.kb = c.u.kb0;
+        if (ahead) enter_ahead(c);
+      }
+    };
+    // row n2 of the [hi rows; lo rows] token tile: the four scale bytes of one k-block are one word
+    auto load_tsf = [&](const Cur& c, int n2) -> uint32_t {
+      const int term = n2 >= BN, n = n2 - term * BN;
+      const uint8_t* sf = term ? a.sf_lo[c.u.side] : a.sf_hi[c.u.side];
+      const int sf_stride = 4 * a.nkb[c.u.side];
+      // not through the read-only path: the second GEMM's scale bytes were written during this launch
+      return (c.u.valid && ((ready_mask >> (c.i & 31)) & 1u) && n2 < 2 * BN && n < c.u.n_e)
+                 ? __ldcg(reinterpret_cast<const uint32_t*>(sf + static_cast<size_t>(c.u.row0 + n) * sf_stride) + c.kb)
+                 : 0x7f7f7f7fu;
+    };
+    Cur cur{0, 0, fused_unit(a, 0)};
+    cur.kb = cur.u.kb0;
+    Cur pre = cur;
+    uint32_t nx[FPP_AHEAD][2];
+    auto prime = [&]() {   // the look-ahead cursor restarts at the loading cursor
+      pre = cur;
+      enter_ahead(pre);
+#pragma unroll
+      for (int d = 0; d < FPP_AHEAD; ++d) {
+        nx[d][0] = load_tsf(pre, lane);
+        nx[d][1] = load_tsf(pre, lane + 32);
+        next(pre, true);
+      }
+    };
+    if (!wait_item(cur.u, true)) ok = false;   // a CTA whose first unit already belongs to the second GEMM
+    prime();
+    const int off = lane * 16;   // row r of the block: (r % 32) * 16 + (r / 32) * 4
+    for (int g = 0; cur.u.valid && ok; ++g) {
+      const int s = g % S, round = g / S;
+      const uint32_t w0 = nx[0][0], w1 = nx[0][1];
+#pragma unroll
+      for (int d = 0; d + 1 < FPP_AHEAD; ++d) {
+        nx[d][0] = nx[d + 1][0];
+        nx[d][1] = nx[d + 1][1];
+      }
+      nx[FPP_AHEAD - 1][0] = load_tsf(pre, lane);
+      nx[FPP_AHEAD - 1][1] = load_tsf(pre, lane + 32);
+      next(pre, true);
+      if (round > 0) ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar.empty[s], (round - 1) & 1, abort_flag));
+      if (!ok) break;
+      if (leader) {
+        mbar_arrive_expect_tx(&bar.full[s], static_cast<uint32_t>(FP4_A_TX + 512 + 2 * BN * 128));
+        const int sd = cur.u.side;
+        tma_load_4d(atile + static_cast<size_t>(s) * FP4_A_BYTES, sd ? &tm_w2 : &tm_w1, &bar.full[s], cur.kb * FP4_KB,
+                    cur.u.tile * MOE_FT, cur.u.e, 0);
+        bulk_load(sfa_s + s * 512,
+                  a.sfa[sd] + ((static_cast<size_t>(cur.u.e) * a.tiles[sd] + cur.u.tile) * a.nkb[sd] + cur.kb) * 512, 512,
+                  &bar.full[s]);
+        uint8_t* bt = btile + static_cast<size_t>(s) * (2 * BN * 128);
+        tma_load_2d(bt, sd ? &tm_hi2 : &tm_hi1, &bar.full[s], cur.kb * FP4_KB, cur.u.row0);
+        tma_load_2d(bt + BN * 128, sd ? &tm_lo2 : &tm_lo1, &bar.full[s], cur.kb * FP4_KB, cur.u.row0);   // lo rows follow hi rows
+      }
+      uint8_t* blk = sfb_s + s * 512;
+      if (lane < 2 * BN) *reinterpret_cast<uint32_t*>(blk + off) = w0;
+      if (BN == 32) *reinterpret_cast<uint32_t*>(blk + off + 4) = w1;
+      fence_proxy_async_smem();   // tcgen05.cp reads the block through the async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar.full[s]);
+      {
+        const int before = cur.i;
+        next(cur, false);
+        // entering a unit whose input the look-ahead cursor did not find complete: wait for it now, then fetch its
+        // scale words again (those fetched ahead were placeholders)
+        if (cur.i != before && cur.u.valid && cur.u.side == 1 && !((ready_mask >> (cur.i & 31)) & 1u)) {
+          if (!wait_item(cur.u, true)) break;
+          prime();
+        }
+      }
+    }
+    if (leader && !ok) {
+      if (!*abort_flag) atomicOr(a.status, B2_DEV_TIMEOUT_EMPTY);
+      *abort_flag = 1;
+    }
+  } else if (warp == 1) {
+    // ===================================== MMA issuer =====================================
+    const bool leader = elect_one();
+    const uint32_t t_sfa = tmem + 2 * BN, t_sfb = t_sfa + 4;
+    bool ok = true;
+    int g = 0;
+    for (int i = 0; ok; ++i) {
+      const FppUnit u = fused_unit(a, i);
+      if (!u.valid) break;
+      for (int kb = u.kb0; kb < u.kb1 && ok; ++kb, ++g) {
+        const int s = g % S;
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar.full[s], (g / S) & 1, abort_flag));
+        // the previous unit's sums must have left the accumulator
+        if (ok && kb == u.kb0 && i > 0) ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar.acc_empty, (i - 1) & 1, abort_flag));
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint64_t da = umma_desc_k128(smem_u32(atile + static_cast<size_t>(s) * FP4_A_BYTES));
+        const uint64_t db = umma_desc_k128(smem_u32(btile + static_cast<size_t>(s) * (2 * BN * 128)));
+        if (leader) {
+          tmem_cp_sf_block(t_sfa, umma_desc_sf_block(smem_u32(sfa_s + s * 512)));
+          tmem_cp_sf_block(t_sfb, umma_desc_sf_block(smem_u32(sfb_s + s * 512)));
+#pragma unroll
+          for (int k = 0; k < FP4_KB / 32; ++k)
+            umma_fp4_fp8(tmem, da + 2 * k, db + 2 * k, umma_idesc_fp4_fp8(MOE_FT, 2 * BN, k, k), t_sfa, t_sfb,
+                         ((kb - u.kb0) | k) != 0);
+          umma_commit(&bar.empty[s]);
+          if (kb == u.kb1 - 1) umma_commit(&bar.acc_full);
+        }
+        __syncwarp();
+      }
+    }
+    if (leader && !ok) {
+      if (!*abort_flag) atomicOr(a.status, B2_DEV_TIMEOUT_MMA);
+      *abort_flag = 1;
+    }
+  } else {
+    // ===================================== epilogue =====================================
+    const int t4 = (warp - 2) * 32 + lane;   // 0..127
+    const int lane_grp = warp & 3;
+    const int fr = lane_grp * 32 + lane;     // feature row of this thread inside the tile
+    const uint32_t trow = tmem + (static_cast<uint32_t>(lane_grp * 32) << 16);
+    __nv_bfloat16* dump = reinterpret_cast<__nv_bfloat16*>(dump_s);
+    bool ok = true;
+    for (int i = 0; ok; ++i) {
+      const FppUnit u = fused_unit(a, i);
+      if (!u.valid) break;
+      const int f = u.tile * MOE_FT + fr;
+      const int n_side = a.N[u.side];
+      const float bias = (f < n_side && u.kh == 0) ? __ldg(a.bias[u.side] + static_cast<size_t>(u.e) * n_side + f) : 0.f;
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar.acc_full, i & 1, abort_flag));
+      if (!ok) {
+        if (lane == 0 && !*abort_flag) atomicOr(a.status, B2_DEV_TIMEOUT_MMA);
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after_sync();
+      float v[32];   // tokens 0 .. BN-1 are meaningful
+      if constexpr (BN == 32) {   // columns 0..31 hold the hi term's sums, columns 32..63 the lo term's
+        float w[32];
+        tmem_ld_32x32_nowait(trow, v);
+        tmem_ld_32x32_nowait(trow + BN, w);
+        tmem_wait_ld();
+#pragma unroll
+        for (int t = 0; t < 32; ++t) v[t] += w[t];
+      } else {                    // one load covers the allocation: hi sums in columns 0..BN-1, lo sums in BN..2BN-1
+        float w[32];
+        tmem_ld_32x32(trow, w);
+#pragma unroll
+        for (int t = 0; t < 32; ++t) v[t] = t < BN ? w[t] + w[(t + BN) & 31] : 0.f;
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar.acc_empty);   // the MMA warp may start the next unit
+
+      if (u.side == 0) {
+        constexpr int OUT_F = MOE_FT / 2;
+        constexpr int PIECES = OUT_F / 8;
+        const int out_n = n_side / 2;
+#pragma unroll
+        for (int t = 0; t < BN; ++t) {
+          const float xv = v[t] + bias;
+          const float other = __shfl_xor_sync(0xffffffffu, xv, 1);
+          if ((lane & 1) == 0) dump[t * OUT_F + (fr >> 1)] = __float2bfloat16_rn(moe_swiglu(xv, other, a.alpha, a.limit));
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        // straight into the form the second GEMM reads: two block-scaled E4M3 terms per row, one scale byte per 32
+        // features (a tile's 64 features are two whole groups); a thread owns 8 features, a quad a group
+        const int total = u.n_e * PIECES;
+        for (int base = 0; base < total; base += 128) {   // uniform trip count: the shuffles need whole warps
+          const int it = base + t4;
+          const bool live = it < total;
+          const int tok = live ? it / PIECES : 0, pc = it - (it / PIECES) * PIECES;
+          float q[8];
+          if (live) {
+            const uint4 p = *reinterpret_cast<const uint4*>(dump + tok * OUT_F + pc * 8);
+            q[0] = bf16lo(p.x); q[1] = bf16hi(p.x); q[2] = bf16lo(p.y); q[3] = bf16hi(p.y);
+            q[4] = bf16lo(p.z); q[5] = bf16hi(p.z); q[6] = bf16lo(p.w); q[7] = bf16hi(p.w);
+          } else {
+#pragma unroll
+            for (int t = 0; t < 8; ++t) q[t] = 0.f;
+          }
+          uint32_t qb[2][2];
+          uint32_t sbyte[2];
+          moe_quant8(q, qb, sbyte);
+          const int col = u.tile * OUT_F + pc * 8;
+          if (live && col + 8 <= out_n) {
+            const size_t row = static_cast<size_t>(u.row0 + tok);
+            *reinterpret_cast<uint2*>(a.q2_hi + row * a.K2 + col) = make_uint2(qb[0][0], qb[0][1]);
+            *reinterpret_cast<uint2*>(a.q2_lo + row * a.K2 + col) = make_uint2(qb[1][0], qb[1][1]);
+            if ((pc & 3) == 0) {
+              const int gq = col >> 5;
+              a.sf2_hi[row * a.sf2_stride + gq] = static_cast<uint8_t>(sbyte[0]);
+              a.sf2_lo[row * a.sf2_stride + gq] = static_cast<uint8_t>(sbyte[1]);
+              if (gq == a.K2 / 32 - 1)   // groups past K2 (the weights are zero there) get a harmless scale of 1
+                for (int gg = gq + 1; gg < a.sf2_stride; ++gg) {
+                  a.sf2_hi[row * a.sf2_stride + gg] = 127;
+                  a.sf2_lo[row * a.sf2_stride + gg] = 127;
+                }
+            }
+          }
+        }
+        __threadfence();   // this thread's rows of the second GEMM's input are visible before the item counts this tile
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // the dump is free for the next unit
+        if (t4 == 0) {
+          asm volatile("fence.proxy.async;" ::: "memory");
+          asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(a.item_done + u.item) : "memory");
+        }
+      } else {
+        constexpr int OUT_F = MOE_FT;
+        constexpr int PIECES = OUT_F / 8;
+        const int out_n = n_side;
         // 128 features x 16 tokens fill the 4 KiB: two passes for 32 tokens
         constexpr int PASS = BN < 16 ? BN : 16;
 #pragma unroll
@@ -1580,6 +1995,94 @@ B2_API int b2_moe_experts_decode_fp4(const void* x, int64_t ldx, const int16_t* 
   int stages = bn_max <= 32 ? 2 : 3;
   if (tunable(TUNE_MOE_FP4_STAGES) >= 2 && tunable(TUNE_MOE_FP4_STAGES) <= FP4_MAX_STAGES) stages = tunable(TUNE_MOE_FP4_STAGES);
   const size_t smem = static_cast<size_t>(stages) * stage_bytes + sizeof(MoeFp4Barriers) + 1024;
+
+  // Measured, whole op, one fused launch against two launches: 128 tokens 105 / 112 us, 256 tokens 132 / 136 us; with the
+  // small parts of small batches the fused kernel loses (4 tokens 65 / 54 us, 32 tokens 124 / 97 us, 64 tokens 118 / 107 us),
+  // so it is the default for 32-token parts only (tunable moe_fp4_fuse: 1 = never, 2 = always).
+  const int fuse = tunable(TUNE_MOE_FP4_FUSE);
+  if (plan.per_sm > 0 && fuse != 1 && (tok == FPP_BN || fuse == 2)) {
+    // both GEMMs in one persistent launch (moe_expert_fp4_fused_kernel); its CTAs wait for one another, so the grid is
+    // sized to be resident as a whole - if that cannot be established the two-launch path below runs instead
+    CUtensorMap tm[2][3];
+    MoeFusedArgs fa;
+    bool maps_ok = true;
+    for (int g = 0; g < 2 && maps_ok; ++g) {
+      const int N = g == 0 ? 2 * intermediate : hidden;
+      const int K = g == 0 ? hidden : intermediate;
+      const int Kp = (K + FP4_KB - 1) / FP4_KB * FP4_KB;
+      const uint64_t wd[4] = {static_cast<uint64_t>(Kp), static_cast<uint64_t>(N), static_cast<uint64_t>(n_experts), 1};
+      const uint64_t wstr[3] = {static_cast<uint64_t>(Kp / 2), static_cast<uint64_t>(N) * (Kp / 2),
+                                static_cast<uint64_t>(n_experts) * N * (Kp / 2)};
+      const uint32_t wbox[4] = {FP4_KB, MOE_FT, 1, 1};
+      const uint64_t xd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(rows)};
+      const uint64_t xstr[1] = {static_cast<uint64_t>(K)};
+      const uint32_t xbox[2] = {FP4_KB, static_cast<uint32_t>(tok)};
+      maps_ok = make_tensor_map(&tm[g][0], CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, g == 0 ? w1_codes : w2_codes, 4, wd, wstr, wbox,
+                                CU_TENSOR_MAP_SWIZZLE_128B) == B2_OK &&
+                make_tensor_map(&tm[g][1], CU_TENSOR_MAP_DATA_TYPE_UINT8, g == 0 ? q_hi : q2_hi, 2, xd, xstr, xbox,
+                                CU_TENSOR_MAP_SWIZZLE_128B) == B2_OK &&
+                make_tensor_map(&tm[g][2], CU_TENSOR_MAP_DATA_TYPE_UINT8, g == 0 ? q_lo : q2_lo, 2, xd, xstr, xbox,
+                                CU_TENSOR_MAP_SWIZZLE_128B) == B2_OK;
+      fa.sfa[g] = static_cast<const uint8_t*>(g == 0 ? w1_sf : w2_sf);
+      fa.sf_hi[g] = g == 0 ? sf_hi : sf2_hi;
+      fa.sf_lo[g] = g == 0 ? sf_lo : sf2_lo;
+      fa.bias[g] = g == 0 ? b1 : b2_;
+      fa.N[g] = N;
+      fa.nkb[g] = Kp / FP4_KB;
+      fa.tiles[g] = (N + MOE_FT - 1) / MOE_FT;
+    }
+    fa.ksplit2 = plan.ksplit;
+    fa.meta = meta;
+    fa.item_done = meta->item_done;
+    fa.out = ybuf;
+    fa.out_half_stride = ybuf2 - ybuf;
+    fa.q2_hi = q2_hi;
+    fa.q2_lo = q2_lo;
+    fa.sf2_hi = sf2_hi;
+    fa.sf2_lo = sf2_lo;
+    fa.K2 = intermediate;
+    fa.sf2_stride = 4 * ((intermediate + FP4_KB - 1) / FP4_KB);
+    fa.tok = tok;
+    fa.alpha = alpha;
+    fa.limit = limit;
+    fa.status = status;
+    int per_sm = plan.per_sm;
+    fa.stages = small_parts ? 5 : FP4_MAX_STAGES / per_sm;
+    const size_t psmem = static_cast<size_t>(fa.stages) * fpp_stage_bytes(tok) + FPP_DUMP_BYTES + sizeof(MoeFppBarriers);
+    auto kern = tok == 8 ? moe_expert_fp4_fused_kernel<8> : (tok == 16 ? moe_expert_fp4_fused_kernel<16> : moe_expert_fp4_fused_kernel<FPP_BN>);
+    int dev = 0, sms = 0, smem_sm = 0, regs_sm = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
+    cudaDeviceGetAttribute(&regs_sm, cudaDevAttrMaxRegistersPerMultiprocessor, dev);
+    cudaFuncAttributes attr;
+    bool fused_ok = maps_ok &&
+                    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(psmem)) == cudaSuccess &&
+                    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) == cudaSuccess &&
+                    cudaFuncGetAttributes(&attr, kern) == cudaSuccess;
+    if (fused_ok) {
+      const int regs_cta = ((attr.numRegs * 32 + 255) / 256 * 256) * (FP4_THREADS / 32);   // allocated per warp in units of 256
+      const int by_smem = static_cast<int>(smem_sm / (psmem + attr.sharedSizeBytes + 1024));   // 1 KiB per CTA is the system's
+      const int by_regs = regs_cta > 0 ? regs_sm / regs_cta : 0;
+      const int by_tmem = 512 / (tok == 32 ? 128 : (tok == 16 ? 64 : 32));
+      per_sm = std::min(per_sm, std::min(by_smem, std::min(by_regs, by_tmem)));
+      fused_ok = per_sm >= 1;
+    } else {
+      (void)cudaGetLastError();
+    }
+    if (fused_ok) {
+      const long long max_units = static_cast<long long>(fa.tiles[0] + fa.tiles[1] * fa.ksplit2) * (rows / tok + n_experts);
+      const unsigned pgrid = static_cast<unsigned>(std::min<long long>(static_cast<long long>(per_sm) * sms, max_units));
+      launch_overlapped(kern, dim3(pgrid), dim3(FP4_THREADS), psmem, st, tm[0][0], tm[0][1], tm[0][2], tm[1][0], tm[1][1], tm[1][2], fa);
+      const int rc = launch_status();
+      if (rc != B2_OK) return rc;
+      if (out)
+        launch_overlapped(moe_combine_kernel, dim3(T), dim3(128), 0, st, static_cast<const __nv_bfloat16*>(ybuf), static_cast<__nv_bfloat16*>(out),
+                          ld_out, hidden, static_cast<int>(T), static_cast<const MoeMeta*>(meta),
+                          static_cast<const __nv_bfloat16*>(plan.ksplit == 2 ? ybuf2 : nullptr));
+      return launch_status();
+    }
+  }
 
   for (int stage = 0; stage < 2; ++stage) {
     const int N = stage == 0 ? 2 * intermediate : hidden;
