@@ -37,7 +37,7 @@ static void init_tunables() {
     g_tunables[TUNE_MOE_FP4_PERSIST] = 4;  // persistent FP4 expert kernel: CTAs per SM (4 / 2 / 1); 0: the one-shot kernel
     g_tunables[TUNE_MOE_FP4_KSPLIT] = 0;   // persistent FP4 expert kernel, last GEMM: 1 = whole k range per unit; else two halves
     g_tunables[TUNE_ATTN_PREFILL_POLY] = 0;   // prefill attention: 2 / 4 = every 2nd / 4th pair of exponentials on the FMA pipe; -1: none; 0: built-in default
-    g_tunables[TUNE_MOE_FP4_FUSE] = 0;     // the two expert GEMMs in one persistent launch: 0 = for 32-token parts, 1 = never, 2 = always
+    g_tunables[TUNE_MOE_FP4_FUSE] = 0;     // the two expert GEMMs in one persistent launch: 0 = for 32-token parts up to 384 tokens, 1 = never, 2 = always
     g_tunables[TUNE_LAUNCH_OVERLAP] = 0;   // 1: decode kernels are launched with programmatic stream serialization
     g_tunables[TUNE_TMA_L2_PROMOTION] = 0;  // 0 none, 1 = 64 B, 2 = 128 B, 3 = 256 B
   }

@@ -1998,9 +1998,10 @@ B2_API int b2_moe_experts_decode_fp4(const void* x, int64_t ldx, const int16_t* 
 
   // Measured, whole op, one fused launch against two launches: 128 tokens 105 / 112 us, 256 tokens 132 / 136 us; with the
   // small parts of small batches the fused kernel loses (4 tokens 65 / 54 us, 32 tokens 124 / 97 us, 64 tokens 118 / 107 us),
-  // so it is the default for 32-token parts only (tunable moe_fp4_fuse: 1 = never, 2 = always).
+  // and so it does with many tokens (512 tokens 214 / 207 us, 1024 tokens 350 / 324 us, 2048 tokens 650 / 603 us): it is
+  // the default for 32-token parts up to 384 tokens (tunable moe_fp4_fuse: 1 = never, 2 = always).
   const int fuse = tunable(TUNE_MOE_FP4_FUSE);
-  if (plan.per_sm > 0 && fuse != 1 && (tok == FPP_BN || fuse == 2)) {
+  if (plan.per_sm > 0 && fuse != 1 && ((tok == FPP_BN && tokens <= 384) || fuse == 2)) {
     // both GEMMs in one persistent launch (moe_expert_fp4_fused_kernel); its CTAs wait for one another, so the grid is
     // sized to be resident as a whole - if that cannot be established the two-launch path below runs instead
     CUtensorMap tm[2][3];
