@@ -1880,8 +1880,10 @@ namespace {
 // experts): up to 4 -> 8, up to 8 -> 16, else 32 (measured, whole op at 32 / 64 / 128 tokens and 32 experts: 8-token
 // parts 96 / 123 / 204 us, 16-token parts 100 / 101 / 128 us, 32-token parts 104 / 108 / 112 us).
 int moe_part_tokens(int64_t tokens, int n_experts) {
-  if (tokens > 128) return 32;
-  return tokens <= n_experts ? 8 : (tokens <= 2 * n_experts ? 16 : 32);
+  int part = tokens <= n_experts ? 8 : (tokens <= 2 * n_experts ? 16 : 32);
+  // the item list holds at most MOE_MAX_ITEMS (expert, part) pairs: rows / part + experts of them in the worst case
+  while (part < 32 && tokens * b2::MOE_TOPK / part + n_experts > b2::MOE_MAX_ITEMS) part *= 2;
+  return part;
 }
 // How b2_moe_experts_decode_fp4 runs under the current tuning knobs; b2_moe_combine_add_rmsnorm must agree with it on
 // where the last GEMM's second partial rows are.
@@ -1967,7 +1969,7 @@ B2_API int b2_moe_experts_decode_fp4(const void* x, int64_t ldx, const int16_t* 
   MoeFp4Plan plan = moe_fp4_plan(tokens, intermediate);
   // a handful of tokens per expert: 8- or 16-token parts, 2 CTAs x 5 stages per SM (tunable moe_fp4_tok = 8 / 16 / 32 forces one)
   int part = tunable(TUNE_MOE_FP4_TOK) == 0 ? moe_part_tokens(tokens, n_experts) : tunable(TUNE_MOE_FP4_TOK);
-  if (tokens > 128 && part < 32) part = 32;   // the item list is sized for 32-token parts beyond that
+  if (part < 32 && tokens * MOE_TOPK / part + n_experts > MOE_MAX_ITEMS) part = 32;   // a forced size the item list cannot hold
   const bool small_parts = plan.per_sm > 0 && (part == 8 || part == 16);
   if (small_parts) {
     plan.tok = part;
