@@ -96,6 +96,30 @@ def test_moe_fp4_kernel_variants_agree_with_the_oracle(knobs):
     assert_parity(_oracle(x, vals, idx, w1, w2), out, f"moe fp4 variant {knobs}")
 
 
+def test_moe_fused_launch_replays_from_a_cuda_graph():
+    """96 tokens on 32 experts take the one-launch path (32-token parts); its per-item completion counts are zeroed by
+    the routing launch of the same call, so a captured call must give the same rows on every replay."""
+    ops = _ops()
+    T, E, H, I = 96, 32, 2880, 2880
+    gen = torch.Generator().manual_seed(4300)
+    x = torch.randn(T, H, generator=gen).bfloat16().cuda()
+    vals, idx, _ = O.topk_softmax(torch.randn(T, E, generator=gen), 4)
+    vals, idx = vals.cuda(), idx.to(torch.int16).cuda()
+    W1, W2 = _packed(_random_experts(gen, E, 2 * I, H)), _packed(_random_experts(gen, E, H, I))
+    eager = ops.moe_experts_decode(x, vals, idx, W1, W2).clone()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = ops.moe_experts_decode(x, vals, idx, W1, W2)
+    for _ in range(3):
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out.view(torch.int16), eager.view(torch.int16))
+    from tritonllm_b200 import _lib
+    assert _lib.device_status() == 0
+
+
 @pytest.mark.parametrize("fp4", FP4)
 def test_moe_all_tokens_one_expert_set(fp4):
     """Every token picks the same four experts: 256 rows per expert, the largest token tile."""
