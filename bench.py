@@ -49,10 +49,11 @@ def algorithmic_bytes(batch: int, visible: int) -> int:
 BYTES_FULL = algorithmic_bytes(B, CTX)
 BYTES_WINDOW = algorithmic_bytes(B, WINDOW)
 BYTES_STEP = (LAYERS // 2) * (BYTES_FULL + BYTES_WINDOW)
-# DRAM bytes one full-causal launch moved in an ncu capture of this kernel on this workload (269,230,848 read +
-# 5,413,376 written).  A recorded constant, not measured in the run: the bench never runs under a profiler.
-NCU_TRAFFIC_FULL = 269230848 + 5413376
-NCU_TRAFFIC_RECORDED = "2026-11-24, attn_decode_kernel with 3 stages of 64 KiB, one CTA per SM"
+# DRAM bytes one full-causal launch moved in an ncu capture of this kernel on this workload (269,243,648 read +
+# 4,486,400 written; the second captured launch: 269,256,960 + 389,888).  A recorded constant, not measured in the
+# run: the bench never runs under a profiler.  Re-recorded after the kernel gained its per-sequence / paged template.
+NCU_TRAFFIC_FULL = 269243648 + 4486400
+NCU_TRAFFIC_RECORDED = "2026-11-25, attn_decode_kernel<false> with 3 stages of 64 KiB, one CTA per SM"
 
 
 def measured_peaks():
