@@ -1,8 +1,13 @@
-// Mixture-of-experts MLP for decode-sized batches (at most 256 tokens): every routed (token, expert)
+// Mixture-of-experts MLP for decode-sized batches: every routed (token, expert)
 // pair runs  a = swiglu(x W1_e + b1_e),  y = (a W2_e + b2_e) * gate,  and a token's output is the sum of
 // its experts' y.  Expert weights stay in MXFP4 in HBM (E2M1 codes, two per byte along K, and one E8M0
-// scale byte per 32 K elements) and are the only large stream: the kernel is weight-bandwidth bound,
-// with the code-to-bf16 conversion on the CUDA cores as the second limit.
+// scale byte per 32 K elements) and are the only large stream: the op is weight-bandwidth bound.
+//
+// Two paths share the routing and the combine.  This first part of the file is the conversion path (at most 256
+// tokens; plain ExpertWeights; codes turned into bf16 on the CUDA cores, which is its second limit).  The FP4
+// tensor-core path (at most 2048 tokens; ExpertWeightsFp4; block-scaled FP4 x FP8 MMAs on the codes as stored) follows
+// further down: the routing + quantise launch, the one-shot kernel, its persistent form, and the fused launch of both
+// GEMMs, each described where it is defined.
 //
 //   moe_route_kernel   one CTA: per-expert token lists (stable: tokens ascending), offsets, gate weights
 //   moe_gather_kernel  copies each routed token's activation row into expert-sorted order
