@@ -120,3 +120,29 @@ def test_scratch_pool_returns_stable_buffers():
     b = scratch_pool.get((2, 3), torch.float32, torch.device("cpu"))
     assert a.data_ptr() == b.data_ptr()
     assert scratch_pool.stats()["num_buffers"] >= 1
+
+
+def test_tuning_knobs_from_the_environment():
+    """TRITONLLM_B200_TUNE is applied when the library is loaded; an unknown knob is an error, not a silent no-op."""
+    import subprocess
+    import sys
+    code = "from tritonllm_b200 import _lib; _lib.load(); print('loaded')"
+    env = dict(os.environ, TRITONLLM_B200_TUNE="moe_fp4_persist=2, unembed_tiles=1")
+    ok = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, cwd=ROOT)
+    assert ok.returncode == 0 and "loaded" in ok.stdout, ok.stderr
+    env["TRITONLLM_B200_TUNE"] = "no_such_knob=1"
+    bad = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, cwd=ROOT)
+    assert bad.returncode != 0 and "TRITONLLM_B200_TUNE" in bad.stderr
+
+
+def test_prompt_sized_moe_takes_over_earlier_with_a_resident_expansion():
+    """The grouped-GEMM path has no per-call expansion to amortise once a weight pair keeps its bf16 copy."""
+    from tritonllm_b200 import ops
+    w1 = ops.ExpertWeightsFp4.__new__(ops.ExpertWeightsFp4)   # the packed weights live on the GPU; the rule reads n and k only
+    w1.n = w1.k = 384                                          # multiples of 192
+    assert not ops._prefill_moe_ok(ops.PREFILL_MOE_MIN_TOKENS - 1, w1, w1)
+    assert ops._prefill_moe_ok(ops.PREFILL_MOE_MIN_TOKENS, w1, w1)
+    w1._expanded = (object(), object(), w1)
+    assert ops._prefill_moe_ok(ops.PREFILL_MOE_MIN_TOKENS_RESIDENT, w1, w1)
+    assert not ops._prefill_moe_ok(ops.PREFILL_MOE_MIN_TOKENS_RESIDENT - 1, w1, w1)
+    assert not ops._prefill_moe_ok(10 ** 6, object(), object())   # plain weights: the conversion path only
