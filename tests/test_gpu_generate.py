@@ -217,6 +217,24 @@ def test_generator_graph_and_eager_agree_and_slide(monkeypatch):
     assert L.device_status() == 0
 
 
+def test_offloaded_experts_give_the_same_tokens():
+    """The CPU-offload mode (experts in pinned host memory, one shared set of GPU buffers filled per layer with the
+    experts the routing chose) computes exactly what the resident model computes, prompt and decode steps alike."""
+    _, G, L = _mods()
+    gen = torch.Generator().manual_seed(29)
+    prompts = torch.randint(0, 1024, (2, 24), generator=gen).cuda()
+    model, _ = _small_model(True, layers=3)
+    ref = G.TokenGenerator(model, context=64, batch_size=2).generate_greedy(prompts, 12).cpu()
+    cache = model.offload_experts(resident_layers=1)
+    assert model.w.layers[0].w1 is None and cache.is_cached(0) and not cache.is_cached(2)
+    tg = G.TokenGenerator(model, context=64, batch_size=2)
+    assert not tg.use_global_cuda_graph
+    got = tg.generate_greedy(prompts, 12).cpu()
+    assert torch.equal(ref, got)
+    assert 0.0 <= cache.hit_rate() <= 1.0 and cache._misses > 0 and cache.host_bytes() > 0
+    assert L.device_status() == 0
+
+
 def test_generator_stops_and_samples():
     _, G, _ = _mods()
     model, _ = _small_model(True, layers=1)

@@ -287,6 +287,22 @@ class Transformer:
                                               alpha=c.rope_ntk_alpha, beta=c.rope_ntk_beta, device=self.device)
         self.sm_scale = 1.0 / (c.head_dim ** 0.5)
         self._zero: dict = {}
+        self.expert_cache = None   # set by offload_experts()
+
+    def offload_experts(self, resident_layers: int = 0):
+        """The reference's ``cpu_offload`` mode (Transformer.from_checkpoint(..., cpu_offload=True), model.py:945-962,
+        1005-1134): every layer's FP4-packed experts move to pinned host memory and one shared set of GPU buffers
+        serves all layers; the first ``resident_layers`` layers keep a copy on the GPU.  The step then has a host
+        synchronisation per layer (which experts were chosen) and cannot be captured in a CUDA graph."""
+        from .expert_cache import ExpertOffloadCache
+        assert all(isinstance(p.w1, ops.ExpertWeightsFp4) for p in self.w.layers), "offload works on FP4-packed experts"
+        cache = ExpertOffloadCache(self.config.num_experts, self.device)
+        for li, p in enumerate(self.w.layers):
+            cache.register_layer(li, p.w1, p.w2, keep_on_gpu=li < resident_layers)
+            p.w1 = p.w2 = None   # the host copy (or the resident copy) is the only one from here on
+            p.offload_layer = li
+        self.expert_cache = cache
+        return cache
 
     def window(self, layer_idx: int) -> int:
         return self.config.sliding_window if layer_idx % 2 == 0 else 0   # model.py:448
@@ -311,18 +327,26 @@ class Transformer:
         vals, idx, _ = ops.topk(logits, self.config.experts_per_token)
         return self._experts(n2, vals, idx, p)
 
+    def _offloaded(self, li: int, idx: torch.Tensor):
+        """(w1, w2) of layer li in the shared GPU buffers, holding at least the experts idx names (a host sync)."""
+        ids = torch.unique(idx).tolist()
+        return self.expert_cache.ensure_experts(li, [e for e in ids if 0 <= e < self.config.num_experts])
+
     def _experts(self, n2, vals, idx, p: LayerWeights) -> torch.Tensor:
         rows = n2.shape[0]
-        block = self.MOE_BLOCK if isinstance(p.w1, ops.ExpertWeightsFp4) else min(256, self.MOE_BLOCK)
+        w1, w2 = p.w1, p.w2
+        if self.expert_cache is not None:   # offload mode: the routed experts are brought into the shared buffers first
+            w1, w2 = self._offloaded(p.offload_layer, idx)
+        block = self.MOE_BLOCK if isinstance(w1, ops.ExpertWeightsFp4) else min(256, self.MOE_BLOCK)
         if rows <= block:
             # a single call may leave the sum over a token's experts to the add + norm that follows it
-            return ops.moe_experts_decode(n2, vals, idx, p.w1, p.w2, limit=self.config.swiglu_limit, defer_combine=True)
-        if ops._prefill_moe_ok(rows, p.w1, p.w2):   # prompt-sized: tokens as the M rows of a grouped GEMM
-            return ops.moe_experts_prefill(n2, vals, idx, p.w1, p.w2, limit=self.config.swiglu_limit)
+            return ops.moe_experts_decode(n2, vals, idx, w1, w2, limit=self.config.swiglu_limit, defer_combine=True)
+        if ops._prefill_moe_ok(rows, w1, w2):   # prompt-sized: tokens as the M rows of a grouped GEMM
+            return ops.moe_experts_prefill(n2, vals, idx, w1, w2, limit=self.config.swiglu_limit)
         out = torch.empty_like(n2)
         for r0 in range(0, rows, block):
             r1 = min(rows, r0 + block)
-            out[r0:r1] = ops.moe_experts_decode(n2[r0:r1], vals[r0:r1], idx[r0:r1], p.w1, p.w2,
+            out[r0:r1] = ops.moe_experts_decode(n2[r0:r1], vals[r0:r1], idx[r0:r1], w1, w2,
                                                 limit=self.config.swiglu_limit)
         return out
 
@@ -466,6 +490,8 @@ class TokenGenerator:
         self.model, self.device, self.batch_size = model, model.device, batch_size
         if use_cuda_graph is None:
             use_cuda_graph = os.getenv("CUDA_GRAPH", "1").strip().lower() not in {"0", "false", "no", "off"}
+        if model.expert_cache is not None:
+            use_cuda_graph = False   # the offload mode asks the host which experts were chosen, once per layer
         self.use_global_cuda_graph = use_cuda_graph
         self.per_sequence = per_sequence or paged
         self.store = model.make_paged_store(batch_size, context, page_size, n_pages) if paged else None

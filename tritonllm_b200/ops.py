@@ -834,7 +834,8 @@ def moe_experts_prefill(x, topk_vals, topk_idx, w1, w2, alpha=1.702, limit=7.0):
         w1b, w2b = resident[0], resident[1]            # expanded by an earlier call
     else:
         size = (w1b.numel() + w2b.numel()) * 2
-        keep = _expanded_budget > 0 and _expanded_used.get(x.device, 0) + size <= _expanded_budget
+        keep = (_expanded_budget > 0 and _expanded_used.get(x.device, 0) + size <= _expanded_budget
+                and not getattr(w1, "_shared_buffer", False))   # views of buffers that change content keep no copy
         if keep:                                       # this pair gets a copy of its own, made once
             w1b, w2b = torch.empty_like(w1b), torch.empty_like(w2b)
         _lib.call("b2_moe_upcast_packed", w1.codes.data_ptr(), w1.sf.data_ptr(), w1b.data_ptr(), e, 2 * inter, hidden, _stream())
