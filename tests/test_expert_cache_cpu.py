@@ -67,3 +67,24 @@ def test_bad_ids_and_shapes_are_refused():
     w1.codes = w1.codes[:, :-1]
     with pytest.raises(AssertionError):
         cache.register_layer(1, w1, w2)
+
+
+def test_victim_store_serves_evicted_experts_and_forgets_the_oldest():
+    cache = ExpertOffloadCache(E, "cpu", pin_memory=False)
+    for li in range(4):
+        cache.register_layer(li, *_layer(li))
+    assert cache.init_victim_store(2) == 2
+    cache.ensure_experts(0, [1])            # miss (host)
+    cache.ensure_experts(1, [1])            # miss; layer 0's expert 1 is saved
+    assert (0, 1) in cache._victim_of and cache._misses == 2
+    cache.ensure_experts(0, [1])            # served by the store: layer 1's copy saved, layer 0's restored
+    assert _slot_tags(cache)[1] == 1 and cache._hits == 1 and cache._misses == 2
+    assert set(cache._victim_of) == {(0, 1), (1, 1)}
+    for buf in cache.gpu:
+        assert torch.all(buf.codes[1] == 1) and torch.all(buf.sf[1] == 101) and torch.all(buf.bias[1] == 1.0)
+    cache.ensure_experts(2, [1])            # layer 0's copy is saved again (already stored: refreshed, now the newest)
+    cache.ensure_experts(3, [1])            # layer 2's copy needs a slot: the oldest entry, layer 1's, goes
+    assert set(cache._victim_of) == {(0, 1), (2, 1)} and cache._misses == 4
+    cache.ensure_experts(1, [1])            # no longer stored: from the host again
+    assert cache._misses == 5 and _slot_tags(cache)[1] == 17
+    assert cache.init_victim_store(0) == 0 and cache.victims is None

@@ -225,13 +225,14 @@ def test_offloaded_experts_give_the_same_tokens():
     prompts = torch.randint(0, 1024, (2, 24), generator=gen).cuda()
     model, _ = _small_model(True, layers=3)
     ref = G.TokenGenerator(model, context=64, batch_size=2).generate_greedy(prompts, 12).cpu()
-    cache = model.offload_experts(resident_layers=1)
+    cache = model.offload_experts(resident_layers=1, victim_slots=6)
     assert model.w.layers[0].w1 is None and cache.is_cached(0) and not cache.is_cached(2)
     tg = G.TokenGenerator(model, context=64, batch_size=2)
     assert not tg.use_global_cuda_graph
     got = tg.generate_greedy(prompts, 12).cpu()
     assert torch.equal(ref, got)
     assert 0.0 <= cache.hit_rate() <= 1.0 and cache._misses > 0 and cache.host_bytes() > 0
+    assert len(cache._victim_of) > 0   # two offloaded layers share the slots: evicted experts went to the second level
     assert L.device_status() == 0
 
 

@@ -7,7 +7,10 @@ the experts its tokens were routed to are copied into their slots of those buffe
 *some* layer, and ``gpu_layer[e]`` says which.  A copy is skipped when the slot already holds this layer's expert (the
 next token of the same layer usually asks for some of the same experts), layers registered with ``keep_on_gpu=True``
 are served by device-to-device copies from a resident copy, and hits and misses are counted as the reference counts
-them.  The reference's victim cache (a second-level GPU store of evicted slots) is not reproduced.
+them.  ``init_victim_store(slots)`` adds the reference's second level (``init_victim_cache`` / ``_vc_put`` / ``_vc_get``,
+expert_cache.py:227-327): before a slot of the shared buffers is overwritten by another layer's expert, its content is
+saved device-to-device into a store of ``slots`` whole experts, least recently used first out, and a later request for
+that (layer, expert) is served from there instead of over PCIe (counted as a hit).
 
 The buffers have the layout the FP4 expert kernels read (``ops.ExpertWeightsFp4``: codes ``[E, N, Kp/2]``, scale
 blocks ``[E, ceil(N/128), Kp/128, 32, 4, 4]``, bias ``[E, N]``), so ``ensure_experts`` returns a pair of
@@ -17,6 +20,7 @@ model) and a host synchronisation per layer for memory, and it cannot run inside
 """
 from __future__ import annotations
 
+from collections import OrderedDict
 from dataclasses import dataclass
 
 import torch
@@ -50,6 +54,9 @@ class ExpertOffloadCache:
         self.gpu_layer: list[int] = [-1] * self.num_experts       # which layer's expert each slot holds
         self._hits = 0
         self._misses = 0
+        self.victims: tuple[_Packed, _Packed] | None = None              # [slots, ...] copies of evicted experts
+        self._victim_of: OrderedDict[tuple[int, int], int] = OrderedDict()   # (layer, expert) -> slot, oldest first
+        self._victim_free: list[int] = []
 
     # ------------------------------------------------------------------ registration
     def _to_host(self, p: _Packed) -> _Packed:
@@ -83,6 +90,44 @@ class ExpertOffloadCache:
     def is_cached(self, layer_idx: int) -> bool:
         return layer_idx in self.resident
 
+    def init_victim_store(self, slots: int) -> int:
+        """Room on the GPU for ``slots`` evicted experts (call after register_layer).  Returns the slots allocated."""
+        assert self.gpu is not None, "register_layer first"
+        slots = max(0, int(slots))
+        if slots == 0:
+            self.victims, self._victim_free = None, []
+            self._victim_of.clear()
+            return 0
+        def room(p):
+            return _Packed(torch.empty((slots,) + tuple(p.codes.shape[1:]), dtype=p.codes.dtype, device=self.device),
+                           torch.empty((slots,) + tuple(p.sf.shape[1:]), dtype=p.sf.dtype, device=self.device),
+                           torch.empty((slots,) + tuple(p.bias.shape[1:]), dtype=p.bias.dtype, device=self.device), p.n, p.k)
+        self.victims = (room(self.gpu[0]), room(self.gpu[1]))
+        self._victim_free = list(range(slots))
+        self._victim_of.clear()
+        return slots
+
+    def _save_victim(self, layer_idx: int, e: int) -> None:
+        """Slot e of the shared buffers (layer_idx's expert) is about to be overwritten: keep a copy."""
+        key = (layer_idx, e)
+        slot = self._victim_of.pop(key, None)
+        if slot is None:
+            slot = self._victim_free.pop() if self._victim_free else self._victim_of.popitem(last=False)[1]
+        self._victim_of[key] = slot   # most recently used
+        for store, buf in zip(self.victims, self.gpu):
+            for d, t in zip(store.expert(slot), buf.expert(e)):
+                d.copy_(t, non_blocking=True)
+
+    def _restore_victim(self, layer_idx: int, e: int) -> bool:
+        slot = self._victim_of.get((layer_idx, e))
+        if slot is None:
+            return False
+        self._victim_of.move_to_end((layer_idx, e))
+        for store, buf in zip(self.victims, self.gpu):
+            for d, t in zip(buf.expert(e), store.expert(slot)):
+                d.copy_(t, non_blocking=True)
+        return True
+
     # ------------------------------------------------------------------ use
     def _views(self):
         from . import ops
@@ -110,6 +155,16 @@ class ExpertOffloadCache:
             if self.gpu_layer[e] == layer_idx:
                 self._hits += counted
                 continue
+            prev = self.gpu_layer[e]
+            if counted and self.victims is not None:
+                # what the slot holds now goes to the victim store first (it may be the very copy asked for next time);
+                # then the store is asked for this layer's expert before the host is
+                if prev >= 0 and prev not in self.resident:
+                    self._save_victim(prev, e)
+                if self._restore_victim(layer_idx, e):
+                    self._hits += 1
+                    self.gpu_layer[e] = layer_idx
+                    continue
             self._misses += counted
             for dst, s in zip(self.gpu, src):
                 for d, t in zip(dst.expert(e), s.expert(e)):
@@ -132,5 +187,5 @@ class ExpertOffloadCache:
         return sum(t.numel() * t.element_size() for pair in self.host.values() for p in pair for t in (p.codes, p.sf, p.bias))
 
     def gpu_bytes(self) -> int:
-        pairs = ([self.gpu] if self.gpu else []) + list(self.resident.values())
+        pairs = ([self.gpu] if self.gpu else []) + list(self.resident.values()) + ([self.victims] if self.victims else [])
         return sum(t.numel() * t.element_size() for pair in pairs for p in pair for t in (p.codes, p.sf, p.bias))

@@ -289,10 +289,11 @@ class Transformer:
         self._zero: dict = {}
         self.expert_cache = None   # set by offload_experts()
 
-    def offload_experts(self, resident_layers: int = 0):
+    def offload_experts(self, resident_layers: int = 0, victim_slots: int = 0):
         """The reference's ``cpu_offload`` mode (Transformer.from_checkpoint(..., cpu_offload=True), model.py:945-962,
         1005-1134): every layer's FP4-packed experts move to pinned host memory and one shared set of GPU buffers
-        serves all layers; the first ``resident_layers`` layers keep a copy on the GPU.  The step then has a host
+        serves all layers; the first ``resident_layers`` layers keep a copy on the GPU and ``victim_slots`` evicted experts
+        are kept in a second-level GPU store.  The step then has a host
         synchronisation per layer (which experts were chosen) and cannot be captured in a CUDA graph."""
         from .expert_cache import ExpertOffloadCache
         assert all(isinstance(p.w1, ops.ExpertWeightsFp4) for p in self.w.layers), "offload works on FP4-packed experts"
@@ -301,6 +302,7 @@ class Transformer:
             cache.register_layer(li, p.w1, p.w2, keep_on_gpu=li < resident_layers)
             p.w1 = p.w2 = None   # the host copy (or the resident copy) is the only one from here on
             p.offload_layer = li
+        cache.init_victim_store(victim_slots)
         self.expert_cache = cache
         return cache
 
